@@ -12,7 +12,9 @@ has one pool of pages (shared by its stages: page p of every stage of the group 
 request and the same positions) and one block table per request.  What a page holds is the need's
 business (`page_shape`): keys and values per kv head, or one latent row per position.  A group with a window gives back
 the pages that lie wholly behind the window as a request advances.  A group of fixed state has one
-slab [stages, slots, ...]; a request's slot is zeroed when the request starts.
+slab [stages, slots, ...]; a request's slot is zeroed when the request starts.  A stage whose mixer is made of
+branches (attention beside a recurrence) hands in a composite need: each of its needs joins the group of its kind,
+and the stage's view is the tuple of the branches' views.
 
 All accounting is host code on plain Python and numpy and is tested without a GPU; only `allocate`
 makes device tensors.
@@ -24,7 +26,7 @@ from typing import Dict, Hashable, List, Optional, Sequence
 import numpy as np
 import torch
 
-from ..parts.cache_need import PAGED_NEEDS, FixedStateNeed, FixedStateView, PagedKVNeed, PagedKVView
+from ..parts.cache_need import PAGED_NEEDS, CompositeNeed, FixedStateNeed, FixedStateView, PagedKVNeed, PagedKVView
 
 
 class OutOfPages(RuntimeError):
@@ -107,10 +109,11 @@ class CacheManager:
         self.max_pages = -(-self.max_context // page_size)
         self.kv_groups: List[_KVGroup] = []
         self.state_groups: List[_StateGroup] = []
-        self.stage_group: Dict[int, tuple] = {}          # stage -> ("kv" | "state", group index, index in group)
-        for stage, need in enumerate(needs):
-            if need is None:
-                continue
+        # stage -> ("kv" | "state", group index, index in group), or ("several", [one such triple or None per branch]) for a
+        # stage whose mixer keeps several things
+        self.stage_group: Dict[int, tuple] = {}
+
+        def join(stage: int, need) -> tuple:
             if isinstance(need, PAGED_NEEDS):
                 groups, kind, make = self.kv_groups, "kv", lambda n: _KVGroup(n, [], num_pages)
             elif isinstance(need, FixedStateNeed):
@@ -123,8 +126,19 @@ class CacheManager:
             else:
                 groups.append(make(need))
                 gi = len(groups) - 1
-            self.stage_group[stage] = (kind, gi, len(groups[gi].stages))
+            place = (kind, gi, len(groups[gi].stages))
             groups[gi].stages.append(stage)
+            return place
+
+        for stage, need in enumerate(needs):
+            if need is None:
+                continue
+            if isinstance(need, CompositeNeed):
+                if any(isinstance(n, CompositeNeed) for n in need.needs):
+                    raise TypeError(f"stage {stage}: a composite need holds plain needs")
+                self.stage_group[stage] = ("several", [None if n is None else join(stage, n) for n in need.needs])
+            else:
+                self.stage_group[stage] = join(stage, need)
         self.lengths: Dict[Hashable, int] = {}
         self.slots: Dict[Hashable, int] = {}
         self._free_slots: List[int] = list(range(max_requests - 1, -1, -1))
@@ -331,7 +345,13 @@ class CacheManager:
     def view(self, stage: int, batch):
         """The cache view of one stage for a step: its pages and the step's block table, or its state
         slab and the step's slots."""
-        kind, gi, idx = self.stage_group[stage]
+        place = self.stage_group[stage]
+        if place[0] == "several":
+            return tuple(None if one is None else self._view(one, batch) for one in place[1])
+        return self._view(place, batch)
+
+    def _view(self, place: tuple, batch):
+        kind, gi, idx = place
         if kind == "kv":
             g = self.kv_groups[gi]
             return PagedKVView(g.device_pool[idx], batch.block_tables[gi], self.page_size, g.need.window)

@@ -102,6 +102,16 @@ class ConfigFields:
             raise ConfigError(f"{self.origin}: key '{key}' is not an array of strings")
         return list(v)
 
+    def number_or_list(self, key: str, required: bool = False) -> Optional[List[float]]:
+        """A constant that is one number for all (heads, say) in some folders and an array, one each, in others."""
+        v, found = self._get(key, None, required)
+        if not found:
+            return None
+        vals = v if isinstance(v, list) else [v]
+        if not all(isinstance(x, (int, float)) and not isinstance(x, bool) for x in vals):
+            raise ConfigError(f"{self.origin}: key '{key}' is not a number or an array of numbers")
+        return [float(x) for x in vals]
+
     def integer_or_list(self, key: str) -> List[int]:
         """A key such as eos_token_id, which is a number in some folders and an array in others."""
         v, found = self._get(key, None, False)

@@ -16,7 +16,8 @@
 // Values may have another size than keys (`vd` features against `hd`): a page then holds the keys of all kv heads,
 // [nkv][page_size][hd], followed by their values, [nkv][page_size][vd].  With `sink` the softmax's denominator is
 // enlarged by one, as if the row saw one more key of score 0 that carries no value: the merge starts its running
-// maximum at 0 and its sum at exp(0 - m), and nothing else changes.
+// maximum at 0 and its sum at exp(0 - m), and nothing else changes.  With `sink_w` the extra key's score is a learned
+// number of the query head, sink_w[h], in place of 0.  With `softcap` c > 0 a score s is replaced by c tanh(s / c).
 #include "common.cuh"
 
 namespace bg {
@@ -44,6 +45,7 @@ struct AttnParams {
     int tile;               // keys per shared-memory tile (32 or 64), divides split
     int bq;                 // rows per query block (upper bound)
     float scale;
+    float softcap;          // c > 0: scores pass c * tanh(s / c); 0: they stay as they are
     unsigned* status;
 };
 
@@ -142,6 +144,7 @@ attention_partial_kernel(AttnParams p) {
                         float dot = 0.0f;
                         for (int d = 0; d < hd; ++d) dot = fmaf(qr[d], kr[d], dot);
                         s[c] = dot * p.scale;
+                        if (p.softcap > 0.0f) s[c] = p.softcap * tanhf(s[c] / p.softcap);
                     }
                 }
                 tmax = fmaxf(tmax, s[c]);
@@ -210,7 +213,8 @@ constexpr int MERGE_GROUPS = 4;
 template <typename TO, int DPL, int BATCH>
 __global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                        const int* __restrict__ positions, TO* __restrict__ out, int out_stride,
-                                       int T, int nh, int hd, int max_splits, int split_arg, int window, int sink) {
+                                       int T, int nh, int hd, int max_splits, int split_arg, int window, int sink,
+                                       const float* __restrict__ sink_w) {
     pdl_launch();
     pdl_wait();
     const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -235,11 +239,12 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o, const f
     for (int g = 0; g < MERGE_GROUPS; ++g) m = fmaxf(m, ms_r[g]);
     for (int sidx = s_lo + 32 * MERGE_GROUPS + lane; sidx <= s_hi; sidx += 32) m = fmaxf(m, part_ml[(prow + sidx) * 2]);
     m = warp_max(m);
-    if (sink) m = fmaxf(m, 0.0f);
+    const float sv = (sink && sink_w) ? sink_w[h] : 0.0f;      // the score of the key without a value
+    if (sink) m = fmaxf(m, sv);
     float acc[DPL];
 #pragma unroll
     for (int i = 0; i < DPL; ++i) acc[i] = 0.0f;
-    float l = sink ? expf(-m) : 0.0f;
+    float l = sink ? expf(sv - m) : 0.0f;
     int grp = 0;
     for (int s0 = s_lo; s0 <= s_hi; s0 += 32, ++grp) {
         // this lane's split of the group of 32: its weight and its share of the sum
@@ -314,7 +319,7 @@ extern "C" int bg_attention_partial(const void* q, int q_dtype, int q_stride, co
                                     int num_pages, int page_size, const int* block_table, int max_pages,
                                     const int* positions, const int* qblk, int n_qblk, float* part_o, float* part_ml,
                                     int max_splits, int n_splits_launch, int nh, int nkv, int hd, int vd, int window, int split,
-                                    int tile, int bq, float scale, unsigned* status, cudaStream_t stream) {
+                                    int tile, int bq, float scale, float softcap, unsigned* status, cudaStream_t stream) {
     if (n_qblk <= 0 || n_splits_launch <= 0) return BG_OK;
     if (nh % nkv != 0 || hd > 32 * ATT_MAX_DPL || vd <= 0 || vd > 32 * ATT_MAX_DPL || (tile != 32 && tile != 64) || split % tile != 0) return BG_ERR_SHAPE;
     if (n_splits_launch > max_splits || n_splits_launch > 65535 || nkv > 65535) return BG_ERR_SHAPE;
@@ -322,7 +327,7 @@ extern "C" int bg_attention_partial(const void* q, int q_dtype, int q_stride, co
     p.q = q; p.q_stride = q_stride; p.kv_pool = kv_pool; p.num_pages = num_pages; p.page_size = page_size;
     p.block_table = block_table; p.max_pages = max_pages; p.positions = positions; p.qblk = qblk;
     p.part_o = part_o; p.part_ml = part_ml; p.max_splits = max_splits; p.nh = nh; p.nkv = nkv; p.hd = hd; p.vd = vd;
-    p.group = nh / nkv; p.window = window; p.split = split; p.tile = tile; p.bq = bq; p.scale = scale; p.status = status;
+    p.group = nh / nkv; p.window = window; p.split = split; p.tile = tile; p.bq = bq; p.scale = scale; p.softcap = softcap; p.status = status;
     size_t smem = attention_smem_bytes(bq, p.group, hd, vd, tile);
     if (smem > 227 * 1024) return BG_ERR_UNSUPPORTED;
     dim3 grid(n_qblk, nkv, n_splits_launch);
@@ -350,7 +355,8 @@ extern "C" int bg_attention_partial(const void* q, int q_dtype, int q_stride, co
 template <typename TO, int NS>
 __global__ void attention_merge_few_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                            const int* __restrict__ positions, TO* __restrict__ out, int out_stride,
-                                           int T, int nh, int hd, int max_splits, int split_arg, int window, int sink) {
+                                           int T, int nh, int hd, int max_splits, int split_arg, int window, int sink,
+                                       const float* __restrict__ sink_w) {
     pdl_launch();
     const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
@@ -377,13 +383,14 @@ __global__ void attention_merge_few_kernel(const float* __restrict__ part_o, con
             v[s][i] = (have && d < hd) ? part_o[(prow + s) * hd + d] : 0.0f;
         }
     }
-    float m = sink ? 0.0f : -INFINITY;
+    const float sv = (sink && sink_w) ? sink_w[h] : 0.0f;
+    float m = sink ? sv : -INFINITY;
 #pragma unroll
     for (int s = 0; s < NS; ++s) {
         if (s < s_lo || s > s_hi) ms[s] = -INFINITY;          // not written for this row: whatever was read is dropped
         m = fmaxf(m, ms[s]);
     }
-    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f}, l = sink ? expf(-m) : 0.0f;
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f}, l = sink ? expf(sv - m) : 0.0f;
 #pragma unroll
     for (int s = 0; s < NS; ++s) {                             // in split order
         if (ms[s] != -INFINITY) {
@@ -414,7 +421,8 @@ template <typename TO>
 __global__ void __launch_bounds__(32 * MERGE_WARPS)
 attention_merge_block_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                              const int* __restrict__ positions, TO* __restrict__ out, int out_stride,
-                             int T, int nh, int hd, int max_splits, int split_arg, int window, int sink) {
+                             int T, int nh, int hd, int max_splits, int split_arg, int window, int sink,
+                                       const float* __restrict__ sink_w) {
     __shared__ float4 acc_s[MERGE_WARPS][32];
     __shared__ float2 ml_s[MERGE_WARPS];
     pdl_launch();
@@ -470,10 +478,11 @@ attention_merge_block_kernel(const float* __restrict__ part_o, const float* __re
     if (lane == 0) ml_s[warp] = make_float2(m, l);
     __syncthreads();
     if (warp != 0) return;
-    float mt = sink ? 0.0f : -INFINITY;
+    const float sv = (sink && sink_w) ? sink_w[h] : 0.0f;
+    float mt = sink ? sv : -INFINITY;
 #pragma unroll
     for (int i = 0; i < MERGE_WARPS; ++i) mt = fmaxf(mt, ml_s[i].x);
-    float lt = sink ? expf(-mt) : 0.0f;
+    float lt = sink ? expf(sv - mt) : 0.0f;
     float4 at = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll
     for (int i = 0; i < MERGE_WARPS; ++i) {                     // in warp order
@@ -494,7 +503,7 @@ attention_merge_block_kernel(const float* __restrict__ part_o, const float* __re
 
 extern "C" int bg_attention_merge(const float* part_o, const float* part_ml, const int* positions, void* out,
                                   int out_dtype, int out_stride, int T, int nh, int hd, int max_splits, int split,
-                                  int window, int sink, cudaStream_t stream) {
+                                  int window, int sink, const float* sink_w, cudaStream_t stream) {
     if (T <= 0) return BG_OK;
     long long warps = (long long)T * nh;
     unsigned blocks = (unsigned)((warps * 32 + 255) / 256);
@@ -509,24 +518,24 @@ extern "C" int bg_attention_merge(const float* part_o, const float* part_ml, con
         // 5 us this way; the decode step of the 1.5B sizes went from 1.372 to 1.214 ms at batch 1, from 1.225 to
         // 1.151 ms at batch 2)
         launch(attention_merge_block_kernel<__nv_bfloat16>, dim3((unsigned)warps), dim3(32 * MERGE_WARPS), 0, stream,
-               part_o, part_ml, positions, (__nv_bfloat16*)out, out_stride, T, nh, hd, max_splits, split, window, sink);
+               part_o, part_ml, positions, (__nv_bfloat16*)out, out_stride, T, nh, hd, max_splits, split, window, sink, sink_w);
     } else if (max_splits <= 8 && hd <= 128) {
         BG_DISPATCH_DTYPE(out_dtype, TO, launch(attention_merge_few_kernel<TO, 8>, dim3(few_blocks), dim3(few_threads), 0, stream,
-            part_o, part_ml, positions, (TO*)out, out_stride, T, nh, hd, max_splits, split, window, sink));
+            part_o, part_ml, positions, (TO*)out, out_stride, T, nh, hd, max_splits, split, window, sink, sink_w));
     } else if (max_splits <= 16 && hd <= 128) {
         BG_DISPATCH_DTYPE(out_dtype, TO, launch(attention_merge_few_kernel<TO, 16>, dim3(few_blocks), dim3(few_threads), 0, stream,
-            part_o, part_ml, positions, (TO*)out, out_stride, T, nh, hd, max_splits, split, window, sink));
+            part_o, part_ml, positions, (TO*)out, out_stride, T, nh, hd, max_splits, split, window, sink, sink_w));
     } else if (block_fits) {
         // bfloat16 rows of few requests with many splits each (the float path keeps one order of summation for
         // every shape of a step, so that its rows do not depend on the batch)
         launch(attention_merge_block_kernel<__nv_bfloat16>, dim3((unsigned)warps), dim3(32 * MERGE_WARPS), 0, stream,
-               part_o, part_ml, positions, (__nv_bfloat16*)out, out_stride, T, nh, hd, max_splits, split, window, sink);
+               part_o, part_ml, positions, (__nv_bfloat16*)out, out_stride, T, nh, hd, max_splits, split, window, sink, sink_w);
     } else if (hd <= 128) {
         BG_DISPATCH_DTYPE(out_dtype, TO, launch(attention_merge_kernel<TO, 4, 16>, dim3(blocks), dim3(256), 0, stream,
-            part_o, part_ml, positions, (TO*)out, out_stride, T, nh, hd, max_splits, split, window, sink));
+            part_o, part_ml, positions, (TO*)out, out_stride, T, nh, hd, max_splits, split, window, sink, sink_w));
     } else {
         BG_DISPATCH_DTYPE(out_dtype, TO, launch(attention_merge_kernel<TO, ATT_MAX_DPL, 4>, dim3(blocks), dim3(256), 0, stream,
-            part_o, part_ml, positions, (TO*)out, out_stride, T, nh, hd, max_splits, split, window, sink));
+            part_o, part_ml, positions, (TO*)out, out_stride, T, nh, hd, max_splits, split, window, sink, sink_w));
     }
     BG_LAUNCH_CHECK();
     return BG_OK;

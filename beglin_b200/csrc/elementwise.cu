@@ -406,7 +406,7 @@ __global__ void swiglu_vec8_kernel(const TI* __restrict__ gu, TO* __restrict__ o
 // cos_sin[t, i] = (cos, sin)(positions[t] * inv_freq[i]), float product of the position converted
 // to float, as qwen_infer.c:791-794 computes it once per token for all layers and heads.
 __global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
-                                  float2* __restrict__ cos_sin, int T, int half) {
+                                  float2* __restrict__ cos_sin, int T, int half, float amplitude) {
     pdl_launch();
     pdl_wait();
     int idx = blockIdx.x * blockDim.x + threadIdx.x;
@@ -415,7 +415,7 @@ __global__ void rope_table_kernel(const int* __restrict__ positions, const float
     float ang = (float)positions[t] * inv_freq[i];
     float s, c;
     sincosf(ang, &s, &c);
-    cos_sin[idx] = make_float2(c, s);
+    cos_sin[idx] = amplitude == 1.0f ? make_float2(c, s) : make_float2(c * amplitude, s * amplitude);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -767,6 +767,61 @@ static int swiglu_in(const void* gu, int parts, size_t part_stride, void* out, i
     return BG_OK;
 }
 
+// out[t, i] = act(z[t, i]) for z = [rows, n] of either type or its float partial sums: the activation of a feed-forward
+// without a gate branch (ACT as in silu_mul).  Eight values a thread where n and the addresses allow it.
+namespace bg {
+template <typename TI, typename TO, int ACT>
+__global__ void activation_kernel(const TI* __restrict__ z, int parts, size_t part_stride, TO* __restrict__ out, size_t total) {
+    pdl_launch();
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    pdl_wait();
+    if (idx >= total) return;
+    out[idx] = from_float<TO>(silu_mul<TO, ACT>(sum_parts(z + idx, parts, part_stride), 1.0f));
+}
+template <typename TI, typename TO, int ACT>
+__global__ void activation_vec8_kernel(const TI* __restrict__ z, int parts, size_t part_stride, TO* __restrict__ out, size_t total8) {
+    pdl_launch();
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    pdl_wait();
+    if (idx >= total8) return;
+    float v[8];
+    load8(z + idx * 8, v);
+    for (int pp = 1; pp < parts; ++pp) {
+        float u[8];
+        load8(z + (size_t)pp * part_stride + idx * 8, u);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] += u[e];
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = silu_mul<TO, ACT>(v[e], 1.0f);
+    store8(out + idx * 8, v);
+}
+}  // namespace bg
+
+template <typename TI, typename TO, int ACT>
+static int activation_launch(const void* z, int parts, size_t part_stride, void* out, size_t total, cudaStream_t stream) {
+    if (total % 8 == 0 && part_stride % 8 == 0 && (uintptr_t)z % 16 == 0 && (uintptr_t)out % 16 == 0) {
+        launch(activation_vec8_kernel<TI, TO, ACT>, dim3((unsigned)((total / 8 + 255) / 256)), dim3(256), 0, stream, (const TI*)z, parts,
+               part_stride, (TO*)out, total / 8);
+    } else {
+        launch(activation_kernel<TI, TO, ACT>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, (const TI*)z, parts,
+               part_stride, (TO*)out, total);
+    }
+    BG_LAUNCH_CHECK();
+    return BG_OK;
+}
+
+extern "C" int bg_activation(const void* z, int in_dtype, int parts, long long part_stride, void* out, int out_dtype, long long total,
+                             int act, cudaStream_t stream) {
+    if (total <= 0) return BG_OK;
+    if (parts < 1 || act < 0 || act > 1) return BG_ERR_SHAPE;
+    BG_DISPATCH_DTYPE(in_dtype, TI, BG_DISPATCH_DTYPE(out_dtype, TO, {
+        if (act == 0) return activation_launch<TI, TO, 0>(z, parts, (size_t)part_stride, out, (size_t)total, stream);
+        return activation_launch<TI, TO, 1>(z, parts, (size_t)part_stride, out, (size_t)total, stream);
+    }));
+    return BG_OK;
+}
+
 extern "C" int bg_swiglu(const void* gu, int in_dtype, int parts, long long part_stride, void* out, int out_dtype,
                          int rows, int im, int block, int act, cudaStream_t stream) {
     if (rows <= 0) return BG_OK;
@@ -776,11 +831,11 @@ extern "C" int bg_swiglu(const void* gu, int in_dtype, int parts, long long part
     return BG_OK;
 }
 
-extern "C" int bg_rope_table(const int* positions, const float* inv_freq, float* cos_sin, int T, int half,
+extern "C" int bg_rope_table(const int* positions, const float* inv_freq, float* cos_sin, int T, int half, float amplitude,
                              cudaStream_t stream) {
     if (T <= 0 || half <= 0) return BG_OK;
     int total = T * half;
-    launch(rope_table_kernel, dim3((total + 255) / 256), dim3(256), 0, stream, positions, inv_freq, (float2*)cos_sin, T, half);
+    launch(rope_table_kernel, dim3((total + 255) / 256), dim3(256), 0, stream, positions, inv_freq, (float2*)cos_sin, T, half, amplitude);
     BG_LAUNCH_CHECK();
     return BG_OK;
 }

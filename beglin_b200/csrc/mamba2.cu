@@ -13,6 +13,7 @@ namespace bg {
 
 __device__ __forceinline__ float softplus32(float z) { return fmaxf(z, 0.0f) + log1pf(expf(-fabsf(z))); }
 __device__ __forceinline__ float silu32(float z) { return z / (1.0f + expf(-z)); }
+__device__ __forceinline__ float sigmoid32(float z) { return 1.0f / (1.0f + expf(-z)); }
 
 // out[t, c] = silu(b[c] + sum_j w[c, j] * in(t - (taps-1-j), c)), in(.) taken from the step's rows of the same
 // request or, further back, from the slot's conv state.  src row = [.. | channels from col0 | ..].
@@ -237,10 +238,11 @@ ssm_scan_kernel(const float* __restrict__ xbc, int channels, const TI* __restric
 
 // out[t, i] = v * rsqrt(mean over i's group of v^2 + eps) * w[i],  v = y[t, i] * silu(z[t, i]); the row is cut
 // into `groups` equal parts, each with a root mean square of its own.  z = src[t, z_col + i].  One block per
-// (row, group).
+// (row, group).  With `mode` 1 the gate stands behind the norm and is a sigmoid: v = y[t, i], and the normed value is
+// multiplied by sigmoid(z[t, i]).
 template <typename TI, typename TW, typename TO>
 __global__ void gated_group_rmsnorm_kernel(const float* __restrict__ y, const TI* __restrict__ src, int src_stride, int z_col,
-                                           const TW* __restrict__ w, float eps, TO* __restrict__ out, int inner, int groups) {
+                                           const TW* __restrict__ w, float eps, TO* __restrict__ out, int inner, int groups, int mode) {
     extern __shared__ float row_buf[];
     __shared__ float red[32];
     pdl_launch();
@@ -251,14 +253,17 @@ __global__ void gated_group_rmsnorm_kernel(const float* __restrict__ y, const TI
     float ss = 0.0f;
     for (int i = threadIdx.x; i < gs; i += blockDim.x) {
         const float z = to_float(src[(size_t)t * src_stride + z_col + i0 + i]);
-        const float v = y[(size_t)t * inner + i0 + i] * silu32(z);
+        const float v = mode ? y[(size_t)t * inner + i0 + i] : y[(size_t)t * inner + i0 + i] * silu32(z);
         row_buf[i] = v;
         ss += v * v;
     }
     ss = block_sum(ss, red);
     const float inv = 1.0f / sqrtf(ss / (float)gs + eps);
-    for (int i = threadIdx.x; i < gs; i += blockDim.x)
-        out[(size_t)t * inner + i0 + i] = from_float<TO>(row_buf[i] * inv * to_float(w[i0 + i]));
+    for (int i = threadIdx.x; i < gs; i += blockDim.x) {
+        float o = row_buf[i] * inv * to_float(w[i0 + i]);
+        if (mode) o *= sigmoid32(to_float(src[(size_t)t * src_stride + z_col + i0 + i]));
+        out[(size_t)t * inner + i0 + i] = from_float<TO>(o);
+    }
 }
 
 // The same with a group's values in registers, eight a run (a group of a multiple of 8 features up to 8192, rows and
@@ -266,24 +271,26 @@ __global__ void gated_group_rmsnorm_kernel(const float* __restrict__ y, const TI
 template <typename TI, typename TW, typename TO, int ITER>
 __global__ void __launch_bounds__(256)
 gated_group_rmsnorm_vec8_kernel(const float* __restrict__ y, const TI* __restrict__ src, int src_stride, int z_col,
-                                const TW* __restrict__ w, float eps, TO* __restrict__ out, int inner, int groups) {
+                                const TW* __restrict__ w, float eps, TO* __restrict__ out, int inner, int groups, int mode) {
     __shared__ float red[32];
     pdl_launch();
     pdl_wait();
     const int t = blockIdx.x, g = blockIdx.y;
     const int gs = inner / groups, g8 = gs / 8;
     const int i0 = g * gs;
-    float v[ITER][8];
+    float v[ITER][8], zg[ITER][8];
     float ss = 0.0f;
 #pragma unroll
     for (int it = 0; it < ITER; ++it) {
         const int c = threadIdx.x + it * 256;
         if (c < g8) {
-            float z[8];
             load8(y + (size_t)t * inner + i0 + c * 8, v[it]);
-            load8(src + (size_t)t * src_stride + z_col + i0 + c * 8, z);
+            load8(src + (size_t)t * src_stride + z_col + i0 + c * 8, zg[it]);
 #pragma unroll
-            for (int k = 0; k < 8; ++k) { v[it][k] *= silu32(z[k]); ss += v[it][k] * v[it][k]; }
+            for (int k = 0; k < 8; ++k) {
+                if (mode) zg[it][k] = sigmoid32(zg[it][k]); else { v[it][k] *= silu32(zg[it][k]); zg[it][k] = 1.0f; }
+                ss += v[it][k] * v[it][k];
+            }
         }
     }
     ss = block_sum(ss, red);
@@ -295,7 +302,7 @@ gated_group_rmsnorm_vec8_kernel(const float* __restrict__ y, const TI* __restric
             float wv[8], ov[8];
             load8(w + i0 + c * 8, wv);
 #pragma unroll
-            for (int k = 0; k < 8; ++k) ov[k] = v[it][k] * inv * wv[k];
+            for (int k = 0; k < 8; ++k) ov[k] = v[it][k] * inv * wv[k] * zg[it][k];
             store8(out + (size_t)t * inner + i0 + c * 8, ov);
         }
     }
@@ -387,7 +394,7 @@ extern "C" int bg_ssm_scan(const float* xbc, int channels, const void* src, int 
 
 extern "C" int bg_gated_group_rmsnorm(const float* y, const void* src, int src_dtype, int src_stride, int z_col, const void* w,
                                       int w_dtype, float eps, void* out, int out_dtype, int n_rows, int inner, int groups,
-                                      cudaStream_t stream) {
+                                      int mode, cudaStream_t stream) {
     if (n_rows <= 0) return BG_OK;
     if (groups <= 0 || inner % groups != 0 || groups > 65535) return BG_ERR_SHAPE;
     const int gs = inner / groups;
@@ -397,9 +404,9 @@ extern "C" int bg_gated_group_rmsnorm(const float* y, const void* src, int src_d
         (uintptr_t)w % 16 == 0 && (uintptr_t)out % 16 == 0) {
         const int iter = (gs / 8 + 255) / 256;
         BG_DISPATCH_DTYPE(src_dtype, TI, BG_DISPATCH_DTYPE(w_dtype, TW, BG_DISPATCH_DTYPE(out_dtype, TO, {
-            if (iter <= 1) launch(gated_group_rmsnorm_vec8_kernel<TI, TW, TO, 1>, dim3(n_rows, groups), dim3(256), 0, stream, y, (const TI*)src, src_stride, z_col, (const TW*)w, eps, (TO*)out, inner, groups);
-            else if (iter <= 2) launch(gated_group_rmsnorm_vec8_kernel<TI, TW, TO, 2>, dim3(n_rows, groups), dim3(256), 0, stream, y, (const TI*)src, src_stride, z_col, (const TW*)w, eps, (TO*)out, inner, groups);
-            else launch(gated_group_rmsnorm_vec8_kernel<TI, TW, TO, 4>, dim3(n_rows, groups), dim3(256), 0, stream, y, (const TI*)src, src_stride, z_col, (const TW*)w, eps, (TO*)out, inner, groups);
+            if (iter <= 1) launch(gated_group_rmsnorm_vec8_kernel<TI, TW, TO, 1>, dim3(n_rows, groups), dim3(256), 0, stream, y, (const TI*)src, src_stride, z_col, (const TW*)w, eps, (TO*)out, inner, groups, mode);
+            else if (iter <= 2) launch(gated_group_rmsnorm_vec8_kernel<TI, TW, TO, 2>, dim3(n_rows, groups), dim3(256), 0, stream, y, (const TI*)src, src_stride, z_col, (const TW*)w, eps, (TO*)out, inner, groups, mode);
+            else launch(gated_group_rmsnorm_vec8_kernel<TI, TW, TO, 4>, dim3(n_rows, groups), dim3(256), 0, stream, y, (const TI*)src, src_stride, z_col, (const TW*)w, eps, (TO*)out, inner, groups, mode);
         })));
         BG_LAUNCH_CHECK();
         return BG_OK;
@@ -409,7 +416,7 @@ extern "C" int bg_gated_group_rmsnorm(const float* y, const void* src, int src_d
         auto kern = gated_group_rmsnorm_kernel<TI, TW, TO>;
         if (smem > BG_SMEM_OPT_IN) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         launch(kern, dim3(n_rows, groups), dim3(threads), smem, stream, y, (const TI*)src, src_stride, z_col, (const TW*)w, eps,
-               (TO*)out, inner, groups);
+               (TO*)out, inner, groups, mode);
     })));
     BG_LAUNCH_CHECK();
     return BG_OK;

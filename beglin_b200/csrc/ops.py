@@ -27,16 +27,17 @@ _SIGNATURES = {
                        _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
     "bg_add_residual": [_c_void_p, _c_void_p, _c_int, _c_ll, _c_void_p],
     "bg_swiglu": [_c_void_p, _c_int, _c_int, _c_ll, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
-    "bg_rope_table": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p],
+    "bg_activation": [_c_void_p, _c_int, _c_int, _c_ll, _c_void_p, _c_int, _c_ll, _c_int, _c_void_p],
+    "bg_rope_table": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_float, _c_void_p],
     "bg_rope_kv_append": [_c_void_p, _c_int, _c_int, _c_int, _c_ll, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p,
                           _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
                           _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
     "bg_attention_plan": [_c_int, _c_int, _c_int, ctypes.POINTER(_c_int), ctypes.POINTER(_c_int)],
     "bg_attention_partial": [_c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int,
                              _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
-                             _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p, _c_void_p],
+                             _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_float, _c_void_p, _c_void_p],
     "bg_attention_merge": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
-                           _c_int, _c_int, _c_int, _c_int, _c_void_p],
+                           _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
     "bg_rmsnorm_add": [_c_void_p, _c_void_p, _c_int, _c_int, _c_ll, _c_void_p, _c_int, _c_float, _c_void_p, _c_int, _c_int,
                        _c_int, _c_void_p],
     "bg_rmsnorm_add_routed": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_float, _c_void_p,
@@ -44,7 +45,8 @@ _SIGNATURES = {
     "bg_cast_rows": [_c_void_p, _c_void_p, _c_int, _c_ll, _c_void_p],
     "bg_qk_norm_rope_append": [_c_void_p, _c_int, _c_int, _c_int, _c_ll, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p,
                                _c_float, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int,
-                               _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
+                               _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p,
+                               _c_void_p],
     "bg_route_logits": [_c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "bg_route_topk": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p],
     "bg_route": [_c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p,
@@ -57,7 +59,11 @@ _SIGNATURES = {
     "bg_gemm_grouped_tc": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int,
                            _c_void_p, _c_int, _c_void_p, _c_void_p],
     "bg_sigmoid_gate": [_c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_ll,
-                        _c_int, _c_int, _c_int, _c_void_p],
+                        _c_int, _c_int, _c_int, _c_int, _c_void_p],
+    "bg_decay_attention": [_c_void_p, _c_int, _c_int, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_ll, _c_void_p,
+                           _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
+    "bg_add_terms_norm": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+                          _c_void_p, _c_void_p, _c_int, _c_float, _c_void_p, _c_void_p, _c_int, _c_void_p],
     "bg_attention_mma_plan": [_c_int, _c_int, _c_int, ctypes.POINTER(_c_int)],
     "bg_attention_mma_partial": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p,
                                  _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
@@ -112,7 +118,7 @@ _SIGNATURES = {
     "bg_ssm_scan": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p,
                     _c_ll, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "bg_gated_group_rmsnorm": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_float, _c_void_p, _c_int,
-                               _c_int, _c_int, _c_int, _c_void_p],
+                               _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "bg_gemm_f32_nt_batched": [_c_void_p, _c_int, _c_ll, _c_void_p, _c_int, _c_ll, _c_void_p, _c_int, _c_ll, _c_int, _c_int,
                                _c_int, _c_int, _c_void_p],
     "bg_sample": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
@@ -401,8 +407,21 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor, block: int = 0, activation:
                                GLU_ACTIVATIONS[activation], _stream()), "swiglu")
 
 
-def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t, i] = (cos, sin)(positions[t] * inv_freq[i]); out is float32 [T, half, 2]."""
+def activation(z: torch.Tensor, out: torch.Tensor, activation: str = "silu") -> None:
+    """out = act(z), z [rows, n] or its float partial sums [parts, rows, n]; act is silu or the tanh form of GELU."""
+    if activation not in GLU_ACTIVATIONS:
+        raise KernelError(f"activation: unknown activation '{activation}' ({', '.join(GLU_ACTIVATIONS)})")
+    _cuda(z, out)
+    parts, stride = _parts(z, "activation: z")
+    if tuple(out.shape) != tuple(z.shape[-2:]) or not z.is_contiguous() or not out.is_contiguous():
+        raise KernelError("activation: z and out contiguous and of one shape")
+    with phase("swiglu"):
+        _check(lib().bg_activation(_p(z), _dt(z), parts, stride, _p(out), _dt(out), out.numel(), GLU_ACTIVATIONS[activation],
+                                   _stream()), "activation")
+
+
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, out: torch.Tensor, amplitude: float = 1.0) -> None:
+    """out[t, i] = amplitude * (cos, sin)(positions[t] * inv_freq[i]); out is float32 [T, half, 2]."""
     _cuda(positions, inv_freq, out)
     _i32(positions, "positions")
     T, half = positions.numel(), inv_freq.numel()
@@ -410,7 +429,7 @@ def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, out: torch.Tenso
             or not out.is_contiguous() or not inv_freq.is_contiguous():
         raise KernelError("rope_table: inv_freq float32 [half], out contiguous float32 [T, half, 2]")
     with phase("rope"):
-        _check(lib().bg_rope_table(_p(positions), _p(inv_freq), _p(out), T, half, _stream()), "rope_table")
+        _check(lib().bg_rope_table(_p(positions), _p(inv_freq), _p(out), T, half, float(amplitude), _stream()), "rope_table")
 
 
 def rope_kv_append(src: torch.Tensor, q_out: torch.Tensor, n_rows: int, nh: int, nkv: int, hd: int, rot: int,
@@ -455,11 +474,13 @@ def attention_wide_from(keys: int = 0) -> int:
 
 
 TC_ROWS_FOR = ("auto", "tcgen05")
+TC_OPTIONS = ()                                # options of the softmax that the tensor-core kernels know besides the plain one
 SINK_KERNELS = ("generic", "tc_rows", "mma_keys", "mma_rows")   # every kernel can take the enlarged denominator (`sink`)
 
 
 def attention_plan(group: int, hd: int, dtype: torch.dtype = torch.float32, decode_only: bool = False,
-                   prefer: str = "auto", page_size: int = 64, vd: Optional[int] = None) -> Tuple[str, int, int]:
+                   prefer: str = "auto", page_size: int = 64, vd: Optional[int] = None, softcap: bool = False,
+                   learned_sink: bool = False) -> Tuple[str, int, int]:
     """(kernel, rows per query block, keys per tile) for these sizes.  Kernels: "mma_keys" (tensor
     cores, one token per block, for steps of single tokens), "mma_rows" (tensor cores, up to 64 rows
     per block) and "generic" (CUDA cores, every size up to head_dim 256, float or bfloat16)."""
@@ -467,11 +488,13 @@ def attention_plan(group: int, hd: int, dtype: torch.dtype = torch.float32, deco
     if prefer not in ("auto", "generic", "mma", "tcgen05"):
         raise KernelError(f"unknown attention kernel choice '{prefer}'")
     vd = hd if vd is None else vd
+    if softcap and "softcap" not in TC_OPTIONS:
+        prefer = "generic"                     # squashed scores are known to the CUDA-core kernel only
     if vd != hd:
         if prefer in ("mma", "tcgen05"):
             raise KernelError(f"the tensor-core attention kernels take values of the keys' size ({hd}), not {vd}")
         prefer = "generic"
-    if dtype == torch.bfloat16 and not decode_only and prefer in TC_ROWS_FOR:
+    if dtype == torch.bfloat16 and not decode_only and prefer in TC_ROWS_FOR and (not learned_sink or "sink_weight" in TC_OPTIONS):
         bq = _c_int(0)
         if L.bg_attention_tc_plan(group, hd, page_size, ctypes.byref(bq)) == 0:
             return "tc_rows", bq.value, 64
@@ -532,7 +555,8 @@ def attention(*args, **kwargs) -> None:
 def _attention(q: torch.Tensor, q_stride: int, kv_pool: torch.Tensor, block_table: torch.Tensor,
               positions: torch.Tensor, qblk: torch.Tensor, n_qblk: int, max_position: int, n_rows: int, nh: int,
               nkv: int, hd: int, window: int, split: int, tile: int, bq: int, scale: float, out: torch.Tensor,
-              status: Optional[torch.Tensor], kernel: str = "generic", vd: Optional[int] = None, sink: bool = False) -> None:
+              status: Optional[torch.Tensor], kernel: str = "generic", vd: Optional[int] = None, sink: bool = False,
+              sink_weight: Optional[torch.Tensor] = None, softcap: float = 0.0) -> None:
     """Paged grouped-query attention of a step's rows; out is [T, nh*hd].  `kernel`, `bq` and `tile`
     come from `attention_plan`; `qblk` must be cut for that `bq`; `max_position` is the largest
     position among the rows (or a bound on it).
@@ -540,8 +564,18 @@ def _attention(q: torch.Tensor, q_stride: int, kv_pool: torch.Tensor, block_tabl
     "generic" cuts the keys into splits of `split` positions (the same boundaries for every request),
     writes partial results and merges them; "mma_keys" (decoding) spreads every request's own keys over
     `decode_splits` CTAs and merges likewise; "mma_rows" and "tc_rows" let one CTA walk all keys of its
-    query block and write `out` directly."""
-    _cuda(q, kv_pool, block_table, positions, qblk, out)
+    query block and write `out` directly.
+
+    `sink`: the softmax's denominator also holds exp(b) for a key that has no value, b = 0, or `sink_weight`[head]
+    (float32 [nh]) when given.  `softcap` c > 0: a score s becomes c tanh(s / c)."""
+    _cuda(q, kv_pool, block_table, positions, qblk, out, sink_weight)
+    if sink_weight is not None:
+        sink = True
+        if sink_weight.dtype != torch.float32 or sink_weight.numel() != nh or not sink_weight.is_contiguous():
+            raise KernelError("attention: the sink's scores are contiguous float32, one per query head")
+    if softcap and kernel != "generic" and "softcap" not in TC_OPTIONS:
+        raise KernelError(f"attention: the kernel '{kernel}' does not squash scores")
+    learned = sink_weight is not None
     _i32(positions, "positions"); _i32(block_table, "block_table")
     if qblk is not None:
         _i32(qblk, "qblk")
@@ -566,6 +600,8 @@ def _attention(q: torch.Tensor, q_stride: int, kv_pool: torch.Tensor, block_tabl
     if out.stride(1) != 1 or out.shape[1] < nh * vd or out.shape[0] < n_rows:
         raise KernelError("attention: out must be [T, nh*vd] with unit inner stride")
     L = lib()
+    if kernel == "tc_rows" and learned and "sink_weight" not in TC_OPTIONS:
+        raise KernelError("attention: the tcgen05 kernel knows the sink of score 0 only")
     if kernel == "tc_rows":
         if q.dtype != torch.bfloat16 or kv_pool.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
             raise KernelError("attention: the tcgen05 kernel takes bfloat16 queries, caches and outputs")
@@ -600,7 +636,7 @@ def _attention(q: torch.Tensor, q_stride: int, kv_pool: torch.Tensor, block_tabl
         _check(L.bg_attention_partial(_p(q), _dt(q), q_stride, _p(kv_pool), _dt(kv_pool), num_pages, page_size,
                                       _p(block_table), block_table.shape[1], _p(positions), _p(qblk), n_qblk,
                                       _p(part_o), _p(part_ml), n_splits, n_splits, nh, nkv, hd, vd, window, split, tile,
-                                      bq, float(scale), _p(status), _stream()), "attention_partial")
+                                      bq, float(scale), float(softcap), _p(status), _stream()), "attention_partial")
     elif kernel in ("mma_keys", "mma_rows"):
         # (the kernels that write finished rows know the plain softmax only: with the enlarged denominator their rows
         # go through partial results, also when there is one range of keys, and the merge adds the sink's share)
@@ -615,7 +651,7 @@ def _attention(q: torch.Tensor, q_stride: int, kv_pool: torch.Tensor, block_tabl
     else:
         raise KernelError(f"unknown attention kernel '{kernel}'")
     _check(L.bg_attention_merge(_p(part_o), _p(part_ml), _p(positions), _p(out), _dt(out), out.stride(0), n_rows, nh,
-                                vd, n_splits, split, window, 1 if sink else 0, _stream()), "attention_merge")
+                                vd, n_splits, split, window, 1 if sink else 0, _p(sink_weight), _stream()), "attention_merge")
 
 
 def gemm_f32_nt(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
@@ -1171,8 +1207,9 @@ def ssm_scan(xbc: torch.Tensor, src: torch.Tensor, dt_col: int, dt_bias: torch.T
 
 
 def gated_group_rmsnorm(y: torch.Tensor, src: torch.Tensor, z_col: int, weight: torch.Tensor, eps: float, groups: int,
-                        out: torch.Tensor) -> None:
-    """out = RMS norm, in `groups` equal parts of a row, of y * silu(src[:, z_col : z_col + inner]), times weight."""
+                        out: torch.Tensor, gate_after: bool = False) -> None:
+    """out = RMS norm, in `groups` equal parts of a row, of y * silu(src[:, z_col : z_col + inner]), times weight.  With
+    `gate_after` the gate stands behind the norm and is a sigmoid: out = norm(y) * weight * sigmoid(src[:, z_col : ...])."""
     _cuda(y, src, weight, out)
     T, inner = y.shape
     if y.dtype != torch.float32 or not y.is_contiguous() or tuple(out.shape) != (T, inner) or not out.is_contiguous():
@@ -1183,7 +1220,7 @@ def gated_group_rmsnorm(y: torch.Tensor, src: torch.Tensor, z_col: int, weight: 
         raise KernelError("gated_group_rmsnorm: one weight per feature")
     with phase("rmsnorm"):
         _check(lib().bg_gated_group_rmsnorm(_p(y), _p(src), _dt(src), src.stride(0), z_col, _p(weight), _dt(weight), float(eps),
-                                            _p(out), _dt(out), T, inner, groups, _stream()), "gated_group_rmsnorm")
+                                            _p(out), _dt(out), T, inner, groups, 1 if gate_after else 0, _stream()), "gated_group_rmsnorm")
 
 
 def rmsnorm_add(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float, lowp: Optional[torch.Tensor] = None) -> None:
@@ -1238,9 +1275,10 @@ def qk_norm_rope_append(src: torch.Tensor, q_out: torch.Tensor, n_rows: int, nh:
                         interleaved: bool, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
                         cos_sin: Optional[torch.Tensor], positions: torch.Tensor, row_req: torch.Tensor,
                         block_table: torch.Tensor, kv_pool: Optional[torch.Tensor], page_size: int,
-                        status: Optional[torch.Tensor], stored: Optional[int] = None) -> None:
+                        status: Optional[torch.Tensor], stored: Optional[int] = None, per_head: bool = False) -> None:
     """Rows [q | k | v | ...] of `src` ([T, W], or float partial sums [parts, T, W]): RMS norm of the whole q row and of
-    the whole k row with the float weights given (None: no norm), rotation of the first `rot` features of every head,
+    the whole k row with the float weights given (None: no norm; with `per_head` every head is normed by itself and the
+    weights have hd values, shared by the heads), rotation of the first `rot` features of every head,
     q into q_out [T, nh*hd], k and v into the paged cache (a page: keys [nkv, page, hd], then values [nkv, page, vd]).
     With `stored` = D every head of q, k and v is stored D features wide, zeros behind its own."""
     qs, ks, vs = (hd, hd, vd) if stored is None else (stored, stored, stored)
@@ -1252,7 +1290,7 @@ def qk_norm_rope_append(src: torch.Tensor, q_out: torch.Tensor, n_rows: int, nh:
         raise KernelError(f"qk_norm_rope_append: rows of {src.shape[-1]} features cannot hold q, k, v ({need})")
     if q_out.stride(1) != 1 or q_out.shape[1] < nh * qs or q_out.shape[0] < n_rows:
         raise KernelError("qk_norm_rope_append: q_out must be [T, nh*hd]")
-    for w, n in ((q_weight, nh * hd), (k_weight, nkv * hd)):
+    for w, n in ((q_weight, hd if per_head else nh * hd), (k_weight, hd if per_head else nkv * hd)):
         if w is not None and (w.dtype != torch.float32 or w.numel() != n or not w.is_contiguous()):
             raise KernelError("qk_norm_rope_append: norm weights are contiguous float32 of the projection's width")
     num_pages = 0
@@ -1267,26 +1305,83 @@ def qk_norm_rope_append(src: torch.Tensor, q_out: torch.Tensor, n_rows: int, nh:
                                             _p(q_weight), _p(k_weight), float(eps), _p(cos_sin), _p(positions), _p(row_req),
                                             _p(block_table), block_table.shape[1], _p(kv_pool),
                                             _dt(kv_pool) if kv_pool is not None else _dt(q_out), num_pages, page_size, n_rows, nh,
-                                            nkv, hd, vd, rot, 1 if interleaved else 0, qs, ks, vs, _p(status), _stream()),
+                                            nkv, hd, vd, rot, 1 if interleaved else 0, qs, ks, vs, 1 if per_head else 0, _p(status), _stream()),
                "qk_norm_rope_append")
 
 
 def sigmoid_gate(out: torch.Tensor, gate: torch.Tensor, col0: int, n: int, src: Optional[torch.Tensor] = None,
-                 vd: Optional[int] = None, head_stride: Optional[int] = None) -> None:
-    """out[t, j] = src[t, (j // vd) * head_stride + j % vd] * sigmoid(gate[t, col0 + j]) for j < n; gate is [T, W] or its float
-    partial sums [parts, T, W].  Without `src`, out itself is gated in place."""
+                 vd: Optional[int] = None, head_stride: Optional[int] = None, gate_per: int = 1) -> None:
+    """out[t, j] = src[t, (j // vd) * head_stride + j % vd] * sigmoid(gate[t, col0 + j // gate_per]) for j < n; gate is [T, W]
+    or its float partial sums [parts, T, W].  Without `src`, out itself is gated in place.  `gate_per` = the size of a head
+    gives every head one gate."""
     _cuda(out, gate, src)
     parts, stride = _parts(gate, "sigmoid_gate: gate")
     T = out.shape[0]
     if src is None:
         src, vd, head_stride = out, n, n
-    if out.dim() != 2 or out.stride(1) != 1 or out.shape[1] < n or gate.stride(-1) != 1 or gate.shape[-2] < T or col0 + n > gate.shape[-1]:
+    if out.dim() != 2 or out.stride(1) != 1 or out.shape[1] < n or gate.stride(-1) != 1 or gate.shape[-2] < T or col0 + -(-n // gate_per) > gate.shape[-1]:
         raise KernelError("sigmoid_gate: out [T, >= n], gate rows that hold n values from col0")
     if src.dtype != out.dtype or src.stride(1) != 1 or src.shape[0] < T or n % vd or src.shape[1] < (n // vd - 1) * head_stride + vd:
         raise KernelError("sigmoid_gate: src of out's type with n / vd heads, head_stride features apart")
     with phase("activation"):
         _check(lib().bg_sigmoid_gate(_p(out), _dt(out), out.stride(0), _p(src), src.stride(0), vd, head_stride, _p(gate), _dt(gate),
-                                     gate.stride(-2), parts, stride, col0, T, n, _stream()), "sigmoid_gate")
+                                     gate.stride(-2), parts, stride, col0, T, n, int(gate_per), _stream()), "sigmoid_gate")
+
+
+def decay_attention(src: torch.Tensor, q_col: int, k_col: int, v_col: int, decay: torch.Tensor, state: torch.Tensor,
+                    slots: torch.Tensor, reqs: torch.Tensor, n_req: int, y: torch.Tensor, H: int, n: int, nv: int) -> None:
+    """Linear attention with a constant decay per head.  `src` [T, W] (or float partial sums [parts, T, W]) holds, from the
+    columns given, the products for q, k ([H, n] each) and v ([H, nv]); q, k, v = silu of them.  Per request (`reqs`
+    [n_req, 3] = request, first row, rows) and head, for its rows in turn: S <- decay[h] S + k v^T, y = S^T q, with S
+    [n, nv] float32 at state[slots[request], h * n * nv ...], read at the start and written back at the end."""
+    _cuda(src, decay, state, slots, reqs, y)
+    _i32(slots, "slots"); _i32(reqs, "reqs")
+    parts, stride = _parts(src, "decay_attention: src")
+    T, W = src.shape[-2:]
+    if src.stride(-1) != 1 or max(q_col + H * n, k_col + H * n, v_col + H * nv) > W:
+        raise KernelError("decay_attention: the rows do not hold q, k and v at the columns given")
+    if decay.dtype != torch.float32 or decay.numel() != H or not decay.is_contiguous():
+        raise KernelError("decay_attention: one float32 decay per head")
+    if state.dtype != torch.float32 or state.dim() != 2 or state.stride(1) != 1 or state.shape[1] < H * n * nv:
+        raise KernelError(f"decay_attention: the state slab is float32 [slots, >= {H * n * nv}]")
+    if y.dtype != torch.float32 or tuple(y.shape) != (T, H * nv) or not y.is_contiguous():
+        raise KernelError(f"decay_attention: y is float32 {(T, H * nv)}")
+    with phase("scan"):
+        _check(lib().bg_decay_attention(_p(src), _dt(src), src.stride(-2), parts, stride, q_col, k_col, v_col, _p(decay), _p(state),
+                                        state.stride(0), _p(slots), _p(reqs), n_req, _p(y), H, n, nv, _stream()), "decay_attention")
+
+
+def add_terms_norm(x: torch.Tensor, terms, assign: bool = False, weight1: Optional[torch.Tensor] = None,
+                   weight2: Optional[torch.Tensor] = None, eps: float = 0.0, out1: Optional[torch.Tensor] = None,
+                   out2: Optional[torch.Tensor] = None) -> None:
+    """x (= or +=) sum_i scale_i * term_i for `terms` = [(tensor, scale), ...], each tensor [T, d] of either type or float
+    partial sums [parts, T, d]; then out1 = rmsnorm(x) * weight1 and out2 = rmsnorm(x) * weight2 when given (one pass
+    over the rows for the sum and both norms).  x is the float32 residual [T, d]."""
+    tensors = [t for t, _ in terms]
+    _cuda(x, weight1, weight2, out1, out2, *tensors)
+    T, d = x.shape
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise KernelError("add_terms_norm: x is contiguous float32")
+    if len(terms) > 6:
+        raise KernelError("add_terms_norm: at most six terms")
+    ptrs, dts, parts, strides, scales = [], [], [], [], []
+    for t, sc in terms:
+        n, st = _parts(t, "add_terms_norm: term")
+        if tuple(t.shape[-2:]) != (T, d) or not t.is_contiguous():
+            raise KernelError("add_terms_norm: a term is contiguous and shaped like x")
+        ptrs.append(t.data_ptr()); dts.append(_dt(t)); parts.append(n); strides.append(st); scales.append(float(sc))
+    for o, w in ((out1, weight1), (out2, weight2)):
+        if o is not None and (w is None or w.numel() != d or not w.is_contiguous() or tuple(o.shape) != (T, d) or not o.is_contiguous()):
+            raise KernelError("add_terms_norm: a normed output is [T, d] and has d weights")
+    if out2 is not None and (out1 is None or out2.dtype != out1.dtype or weight2.dtype != weight1.dtype):
+        raise KernelError("add_terms_norm: the second normed output comes with a first of the same types")
+    k = len(terms)
+    arr = lambda ct, vals: (ct * max(k, 1))(*vals) if vals else (ct * 1)()
+    with phase("rmsnorm" if out1 is not None else "residuals"):
+        _check(lib().bg_add_terms_norm(_p(x), T, d, 1 if assign else 0, k, arr(_c_void_p, ptrs), arr(_c_int, dts), arr(_c_int, parts),
+                                       arr(_c_ll, strides), arr(_c_float, scales), _p(weight1), _p(weight2),
+                                       _dt(weight1) if weight1 is not None else F32, float(eps), _p(out1), _p(out2),
+                                       _dt(out1) if out1 is not None else F32, _stream()), "add_terms_norm")
 
 
 # ---------------------------------------------------------------------------------------------------- routed experts

@@ -22,6 +22,7 @@ struct QkNormRopeParams {
     const void* src; int src_stride; int parts; size_t part_stride;
     void* q_out; int q_stride;
     const float* wq; const float* wk; float eps;            // null: no norm
+    int per_head;                                            // 1: every head has a root mean square of its own, and wq, wk hold hd weights
     const float* cos_sin;                                    // [T][rot/2][2] or null when rot == 0
     const int* positions; const int* row_req; const int* block_table; int max_pages;
     void* pool; int num_pages, page_size;                    // null pool: the rows hold queries only
@@ -29,6 +30,21 @@ struct QkNormRopeParams {
     int qs, ks, vs;                                          // stored width of a query, key and value head (>= hd, hd, vd)
     unsigned* status;
 };
+
+// Every head of the staged queries and keys divided by its own root mean square and multiplied by the weights of its
+// kind (one vector of hd weights for all query heads, one for all key heads).  A warp per head.
+__device__ __forceinline__ void norm_heads_in_place(float* qk_s, const QkNormRopeParams& p, int n_heads) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+    for (int h = warp; h < n_heads; h += n_warps) {
+        float* v = qk_s + (size_t)h * p.hd;
+        const float* w = h < p.nh ? p.wq : p.wk;
+        float ss = 0.0f;
+        for (int f = lane; f < p.hd; f += 32) ss += v[f] * v[f];
+        ss = warp_sum(ss);
+        const float inv = 1.0f / sqrtf(ss / (float)p.hd + p.eps);
+        for (int f = lane; f < p.hd; f += 32) v[f] = v[f] * inv * w[f];
+    }
+}
 
 template <typename TS, typename TQ, typename TC>
 __global__ void __launch_bounds__(256) qk_norm_rope_append_kernel(QkNormRopeParams p) {
@@ -61,7 +77,10 @@ __global__ void __launch_bounds__(256) qk_norm_rope_append_kernel(QkNormRopePara
         qk_s[i] = v;
         if (i < qd) ssq += v * v; else ssk += v * v;
     }
-    if (p.wq) {
+    if (p.wq && p.per_head) {
+        __syncthreads();
+        norm_heads_in_place(qk_s, p, p.nh + (p.pool ? p.nkv : 0));
+    } else if (p.wq) {
         ssq = block_sum(ssq, red);
         ssk = block_sum(ssk, red);
         const float inv_q = 1.0f / sqrtf(ssq / (float)qd + p.eps);
@@ -149,7 +168,11 @@ __global__ void __launch_bounds__(256) qk_norm_rope_append_vec8_kernel(QkNormRop
         if (i < qd) ssq += ss; else ssk += ss;
     }
     float inv_q = 1.0f, inv_k = 1.0f;
-    if (p.wq) {
+    const bool whole = p.wq && !p.per_head;                  // the norm over the whole row is applied on the way out
+    if (p.wq && p.per_head) {
+        __syncthreads();
+        norm_heads_in_place(qk_s, p, p.nh + (p.pool ? p.nkv : 0));
+    } else if (p.wq) {
         ssq = block_sum(ssq, red);
         ssk = block_sum(ssk, red);
         inv_q = 1.0f / sqrtf(ssq / (float)qd + p.eps);
@@ -164,7 +187,7 @@ __global__ void __launch_bounds__(256) qk_norm_rope_append_vec8_kernel(QkNormRop
         const int j = is_q ? i : i - qd;
         const int h = j / p.hd, f = j - h * p.hd;
         const float inv = is_q ? inv_q : inv_k;
-        const float* w = p.wq ? (is_q ? p.wq + j : p.wk + j) : nullptr;
+        const float* w = whole ? (is_q ? p.wq + j : p.wk + j) : nullptr;
         float v[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) v[e] = w ? qk_s[i + e] * inv * w[e] : qk_s[i + e];
@@ -207,12 +230,13 @@ __global__ void __launch_bounds__(256) qk_norm_rope_append_vec8_kernel(QkNormRop
             store8(pool + v_base + (size_t)(i / vpad) * p.page_size * p.vs + p.vd + 8 * (i % vpad), zero);
 }
 
-// out[t][j] = src[t][(j / vd) * head_stride + j % vd] * sigmoid(gate[t][col0 + j]) for j < n: the gate is a column range of
-// a wider row (or of its partial sums); the source's heads may be stored wider than they are (out == src when they are not).
+// out[t][j] = src[t][(j / vd) * head_stride + j % vd] * sigmoid(gate[t][col0 + j / gate_per]) for j < n: the gate is a column
+// range of a wider row (or of its partial sums), one number per feature (gate_per 1) or one per head (gate_per = vd); the
+// source's heads may be stored wider than they are (out == src when they are not).
 template <typename TG, typename TO>
 __global__ void sigmoid_gate_kernel(TO* __restrict__ out, int out_stride, const TO* __restrict__ src, int src_stride, int vd,
                                     int head_stride, const TG* __restrict__ gate, int gate_stride, int parts,
-                                    size_t part_stride, int col0, int rows, int n) {
+                                    size_t part_stride, int col0, int rows, int n, int gate_per) {
     pdl_launch();
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const bool idle = idx >= (size_t)rows * n;
@@ -220,7 +244,7 @@ __global__ void sigmoid_gate_kernel(TO* __restrict__ out, int out_stride, const 
     const int j = idle ? 0 : (int)(idx - t * n);
     pdl_wait();
     if (idle) return;
-    const float g = sum_parts(gate + t * gate_stride + col0 + j, parts, part_stride);
+    const float g = sum_parts(gate + t * gate_stride + col0 + j / gate_per, parts, part_stride);
     const float v = to_float(src[t * src_stride + (size_t)(j / vd) * head_stride + j % vd]);
     out[t * out_stride + j] = from_float<TO>(v / (1.0f + expf(-g)));
 }
@@ -229,7 +253,7 @@ __global__ void sigmoid_gate_kernel(TO* __restrict__ out, int out_stride, const 
 template <typename TG, typename TO>
 __global__ void sigmoid_gate_vec8_kernel(TO* __restrict__ out, int out_stride, const TO* __restrict__ src, int src_stride, int vd,
                                          int head_stride, const TG* __restrict__ gate, int gate_stride, int parts,
-                                         size_t part_stride, int col0, int rows, int n) {
+                                         size_t part_stride, int col0, int rows, int n, int gate_per) {
     pdl_launch();
     const int n8 = n >> 3;
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -239,12 +263,18 @@ __global__ void sigmoid_gate_vec8_kernel(TO* __restrict__ out, int out_stride, c
     pdl_wait();
     if (idle) return;
     float g[8], v[8];
-    load8(gate + t * gate_stride + col0 + j, g);
-    for (int pp = 1; pp < parts; ++pp) {
-        float u[8];
-        load8(gate + (size_t)pp * part_stride + t * gate_stride + col0 + j, u);
+    if (gate_per > 1) {                       // one gate for the eight values (gate_per is a multiple of 8)
+        const float one = sum_parts(gate + t * gate_stride + col0 + j / gate_per, parts, part_stride);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) g[e] += u[e];
+        for (int e = 0; e < 8; ++e) g[e] = one;
+    } else {
+        load8(gate + t * gate_stride + col0 + j, g);
+        for (int pp = 1; pp < parts; ++pp) {
+            float u[8];
+            load8(gate + (size_t)pp * part_stride + t * gate_stride + col0 + j, u);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) g[e] += u[e];
+        }
     }
     load8(src + t * src_stride + (size_t)(j / vd) * head_stride + j % vd, v);
 #pragma unroll
@@ -279,8 +309,8 @@ extern "C" int bg_qk_norm_rope_append(const void* src, int src_dtype, int src_st
                                       void* q_out, int q_dtype, int q_stride, const float* wq, const float* wk, float eps,
                                       const float* cos_sin, const int* positions, const int* row_req, const int* block_table,
                                       int max_pages, void* pool, int cache_dtype, int num_pages, int page_size, int T, int nh,
-                                      int nkv, int hd, int vd, int rot, int interleaved, int qs, int ks, int vs, unsigned* status,
-                                      cudaStream_t stream) {
+                                      int nkv, int hd, int vd, int rot, int interleaved, int qs, int ks, int vs, int per_head,
+                                      unsigned* status, cudaStream_t stream) {
     if (T <= 0) return BG_OK;
     if (rot < 0 || rot > hd || rot % 2 || parts < 1 || (rot > 0 && !cos_sin) || ((wq == nullptr) != (wk == nullptr))) return BG_ERR_SHAPE;
     if (qs < hd || ks < hd || vs < vd) return BG_ERR_SHAPE;
@@ -289,7 +319,7 @@ extern "C" int bg_qk_norm_rope_append(const void* src, int src_dtype, int src_st
     p.src = src; p.src_stride = src_stride; p.parts = parts; p.part_stride = (size_t)part_stride; p.q_out = q_out;
     p.q_stride = q_stride; p.wq = wq; p.wk = wk; p.eps = eps; p.cos_sin = cos_sin; p.positions = positions; p.row_req = row_req;
     p.block_table = block_table; p.max_pages = max_pages; p.pool = pool; p.num_pages = num_pages; p.page_size = page_size;
-    p.nh = nh; p.nkv = nkv; p.hd = hd; p.vd = vd; p.rot = rot; p.interleaved = interleaved; p.qs = qs; p.ks = ks; p.vs = vs; p.status = status;
+    p.nh = nh; p.nkv = nkv; p.hd = hd; p.vd = vd; p.rot = rot; p.interleaved = interleaved; p.qs = qs; p.ks = ks; p.vs = vs; p.per_head = per_head; p.status = status;
     if (!pool) cache_dtype = q_dtype;
     if (cache_dtype != q_dtype) return BG_ERR_DTYPE;            // queries and cache are both of the compute type
     if (q_dtype == BG_DTYPE_F32) {
@@ -302,26 +332,26 @@ extern "C" int bg_qk_norm_rope_append(const void* src, int src_dtype, int src_st
 
 extern "C" int bg_sigmoid_gate(void* out, int out_dtype, int out_stride, const void* src, int src_stride, int vd, int head_stride,
                                const void* gate, int gate_dtype, int gate_stride, int parts, long long part_stride, int col0,
-                               int rows, int n, cudaStream_t stream) {
+                               int rows, int n, int gate_per, cudaStream_t stream) {
     if (rows <= 0 || n <= 0) return BG_OK;
-    if (parts < 1 || vd <= 0 || head_stride < vd) return BG_ERR_SHAPE;
+    if (parts < 1 || vd <= 0 || head_stride < vd || gate_per < 1) return BG_ERR_SHAPE;
     const size_t total = (size_t)rows * n;
     const unsigned blocks = (unsigned)((total + 255) / 256);
     const bool vec = out_dtype == BG_DTYPE_BF16 && n % 8 == 0 && vd % 8 == 0 && head_stride % 8 == 0 && out_stride % 8 == 0 &&
-                     src_stride % 8 == 0 && gate_stride % 8 == 0 && col0 % 8 == 0 && part_stride % 8 == 0 &&
-                     (uintptr_t)out % 16 == 0 && (uintptr_t)src % 16 == 0 && (uintptr_t)gate % 16 == 0;
+                     src_stride % 8 == 0 && (gate_per > 1 ? gate_per % 8 == 0 : (gate_stride % 8 == 0 && col0 % 8 == 0 && part_stride % 8 == 0)) &&
+                     (uintptr_t)out % 16 == 0 && (uintptr_t)src % 16 == 0 && (gate_per > 1 || (uintptr_t)gate % 16 == 0);
     if (vec) {
         const unsigned vblocks = (unsigned)((total / 8 + 255) / 256);
         BG_DISPATCH_DTYPE(gate_dtype, TG,
             launch(sigmoid_gate_vec8_kernel<TG, __nv_bfloat16>, dim3(vblocks), dim3(256), 0, stream, (__nv_bfloat16*)out, out_stride,
                    (const __nv_bfloat16*)src, src_stride, vd, head_stride, (const TG*)gate, gate_stride, parts, (size_t)part_stride,
-                   col0, rows, n));
+                   col0, rows, n, gate_per));
         BG_LAUNCH_CHECK();
         return BG_OK;
     }
     BG_DISPATCH_DTYPE(gate_dtype, TG, BG_DISPATCH_DTYPE(out_dtype, TO,
         launch(sigmoid_gate_kernel<TG, TO>, dim3(blocks), dim3(256), 0, stream, (TO*)out, out_stride, (const TO*)src, src_stride, vd,
-               head_stride, (const TG*)gate, gate_stride, parts, (size_t)part_stride, col0, rows, n)));
+               head_stride, (const TG*)gate, gate_stride, parts, (size_t)part_stride, col0, rows, n, gate_per)));
     BG_LAUNCH_CHECK();
     return BG_OK;
 }

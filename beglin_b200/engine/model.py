@@ -34,7 +34,15 @@ class DecoderModel:
                     if name in tensors:
                         mine[role.name] = tensors[name]
                 parts[slot] = cls(pspec, mine, ctx)
-            self.blocks.append(registry.block_class(layer.block)(**parts))
+            self.blocks.append(registry.block_class(layer.block)(**parts, **getattr(layer, "block_args", {})))
+        # parts that stand in front of stages (the input of a pass of a repeated run of layers)
+        self.entries = []
+        for entry in spec.entries:
+            cls = registry.entry_class(entry.part.kind)
+            mine = {role.name: tensors[entry.names[role.name]] for role in cls.expected_tensors(entry.part)
+                    if entry.names[role.name] in tensors}
+            self.entries.append(cls(entry.part, mine, ctx))
+        self.keep_origin = any(getattr(e, "needs_origin", False) for e in self.entries)
         self.final_norm = registry.norm_class(spec.final_norm.kind)(
             spec.final_norm, {"weight": tensors[spec.final_norm_name]}, ctx)
         head_bias = None if spec.head_bias_name is None else tensors[spec.head_bias_name]
@@ -71,6 +79,9 @@ class DecoderModel:
         def walk(obj, depth=0):
             if isinstance(obj, torch.Tensor):
                 add(obj)
+            elif isinstance(obj, (list, tuple)):
+                for v in obj:
+                    walk(v, depth)
             elif depth < 3 and hasattr(obj, "__dict__"):
                 for k, v in vars(obj).items():
                     if k in ("ctx", "spec", "bias_c", "embed"):
@@ -80,6 +91,8 @@ class DecoderModel:
         for b in self.blocks:
             for part in vars(b).values():
                 walk(part)
+        for e in self.entries:
+            walk(e)
         walk(self.final_norm)
         walk(self.head)
         return total
@@ -94,7 +107,11 @@ class DecoderModel:
         x = torch.empty((batch.n_rows, self.spec.hidden), dtype=torch.float32, device=self.ctx.device)
         ops.embed_gather(self.embed, batch.token_ids, x, self.ctx.status, scale=self.spec.embed_scale)
         stream = ResidualStream(x)
+        if self.keep_origin:
+            stream.origin = x.clone()
         for si, stage in enumerate(self.spec.order):
+            if stage.enter is not None:
+                self.entries[stage.enter].forward(stream, batch)
             owner = si if stage.cache is None else stage.cache
             view = cache.view(owner, batch) if owner in cache.stage_group else None
             self.blocks[stage.layer].forward(stream, batch, view)
@@ -102,9 +119,13 @@ class DecoderModel:
                 rows = stream.x.clone()
                 if stream.pending is not None:
                     rows += stream.pending.float().reshape(-1, *rows.shape).sum(0)
+                if stream.terms is not None:
+                    for t, c in stream.terms.items:
+                        rows += c * t.float().reshape(-1, *rows.shape).sum(0)
                 tap(si, rows)
         if batch.n_logit_rows == 0:
             return None
+        stream.settle()
         h = self.final_norm.add_norm(stream.x, stream.pending, rows=batch.logit_rows, update=False)
         logits = self.head(h, out_dtype=torch.float32)
         if self.spec.logit_softcap > 0.0:

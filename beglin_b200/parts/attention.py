@@ -8,8 +8,9 @@ product.  All rows' keys and values are in the cache before any row's attention 
 (qwen_infer.c:2017-2023), which is what makes a prompt portion causal.
 
 Options of the spec, each off for the plain form: values of another size than keys; an RMS norm of the whole query
-row and of the whole key row of a token before the rotation; a softmax whose denominator is enlarged by one; a gate,
-sigmoid of a further product of the mixer's input, on the joined heads before the output product.  The gate's matrix is
+row and of the whole key row of a token before the rotation, or of every head by itself; a softmax whose denominator is
+enlarged by one, or by exp of a learned number per head; scores squashed by c tanh(s / c); a gate, sigmoid of a further
+product of the mixer's input, on the joined heads before the output product, feature by feature or one number per head.  The gate's matrix is
 one more block of rows of the one q/k/v product.  With any of the first two the kernel that norms, rotates and appends
 is `qk_norm_rope_append`.
 """
@@ -49,11 +50,14 @@ class GQAAttention:
         if spec.out_bias:
             roles.append(TensorRole("o_proj.bias", (spec.hidden,), role="bias"))
         if spec.qk_norm is not None:
-            roles.append(TensorRole("q_norm.weight", (qd,), role="scale"))
+            per_head = spec.qk_norm == "head"          # one vector of head_dim weights for all heads of a kind
+            roles.append(TensorRole("q_norm.weight", (spec.head_dim if per_head else qd,), role="scale"))
             if spec.own_kv:
-                roles.append(TensorRole("k_norm.weight", (kvd,), role="scale"))
+                roles.append(TensorRole("k_norm.weight", (spec.head_dim if per_head else kvd,), role="scale"))
         if spec.gate is not None:
-            roles.append(TensorRole("g_proj.weight", (od, spec.hidden), True, True))
+            roles.append(TensorRole("g_proj.weight", (spec.n_heads if spec.gate == "head" else od, spec.hidden), True, True))
+        if spec.sink == "learned":
+            roles.append(TensorRole("sink", (spec.n_heads,)))
         return roles
 
     cache_need_takes_context = True        # cache_need(spec, ctx): what a page holds depends on the compute type
@@ -90,10 +94,14 @@ class GQAAttention:
         if spec.head_dim % 2 or spec.head_dim > 256:
             raise ValueError(f"head_dim={spec.head_dim} must be even and at most 256")
         self.spec, self.ctx = spec, ctx
-        if spec.qk_norm not in (None, "projection"):
-            raise ValueError(f"unknown query/key norm '{spec.qk_norm}' (projection)")
-        if spec.gate not in (None, "elementwise"):
-            raise ValueError(f"unknown output gate '{spec.gate}' (elementwise)")
+        if spec.qk_norm not in (None, "projection", "head"):
+            raise ValueError(f"unknown query/key norm '{spec.qk_norm}' (projection, head)")
+        if spec.gate not in (None, "elementwise", "head"):
+            raise ValueError(f"unknown output gate '{spec.gate}' (elementwise, head)")
+        if spec.sink not in (False, True, "learned"):
+            raise ValueError(f"unknown sink '{spec.sink}' (False, True, learned)")
+        if spec.score_cap is not None and not spec.score_cap > 0.0:
+            raise ValueError(f"score_cap={spec.score_cap} must be positive")
         self.nh, self.nkv, self.hd, self.vd = spec.n_heads, spec.n_kv_heads, spec.head_dim, spec.value_dim
         if self.vd <= 0 or self.vd > 256:
             raise ValueError(f"v_head_dim={self.vd} must be positive and at most 256")
@@ -101,15 +109,19 @@ class GQAAttention:
         self.od = self.nh * self.vd
         # what the plain form does not have: the step between product and attention is then a kernel of its own
         self.extended = spec.qk_norm is not None or self.vd != self.hd or spec.gate is not None
-        if self.extended and (spec.qkv_bias and spec.gate is not None or not spec.own_kv):
-            raise ValueError("the extended attention has a cache of its own and no bias beside a gate")
+        if self.extended and not spec.own_kv:
+            raise ValueError("the extended attention has a cache of its own")
         names = ["q_proj"] + (["k_proj", "v_proj"] if spec.own_kv else [])
         w = torch.cat([tensors[n + ".weight"] for n in names] + ([tensors["g_proj.weight"]] if spec.gate else []), dim=0)
         b = torch.cat([tensors[n + ".bias"].float() for n in names], dim=0) if spec.qkv_bias else None
+        if b is not None and spec.gate:                # the gate's rows of the one product have no bias
+            b = torch.cat([b, torch.zeros(tensors["g_proj.weight"].shape[0], dtype=b.dtype, device=b.device)])
         self.gate_col = self.qd + (self.kvd + self.nkv * self.vd if spec.own_kv else 0)
         f32 = lambda t: t.to(device=ctx.device, dtype=torch.float32).contiguous()
         self.q_norm = f32(tensors["q_norm.weight"]) if spec.qk_norm else None
         self.k_norm = f32(tensors["k_norm.weight"]) if spec.qk_norm else None
+        self.sink_weight = f32(tensors["sink"]) if spec.sink == "learned" else None
+        self.score_cap = float(np.float32(spec.score_cap)) if spec.score_cap is not None else 0.0
         self.qkv = Linear(w, b, ctx, label="proj_qkv")
         self.o_proj = Linear(tensors["o_proj.weight"], tensors.get("o_proj.bias") if spec.out_bias else None, ctx,
                              label="proj_o")
@@ -120,7 +132,8 @@ class GQAAttention:
         self.stored = self.stored_head(spec, ctx)
         khd, kvd_ = (self.hd, self.vd) if self.stored is None else (self.stored, self.stored)     # what the kernels see
         self.plans = {d: ops.attention_plan(self.nh // self.nkv, khd, ctx.cache_dtype, d, ctx.attention,
-                                            ctx.page_size, vd=kvd_) for d in (False, True)}
+                                            ctx.page_size, vd=kvd_, softcap=self.score_cap > 0.0,
+                                            learned_sink=self.sink_weight is not None) for d in (False, True)}
         self.window = int(spec.window) if spec.window else 0
         # the fused q/k/v product can rotate and append itself: whole heads rotated in halves, a cache of its own
         # in bfloat16
@@ -142,7 +155,8 @@ class GQAAttention:
             ops.qk_norm_rope_append(qkv, q, T, self.nh, self.nkv, self.hd, self.vd, self.position.rotary_dim,
                                     self.position.interleaved, self.q_norm, self.k_norm, self.spec.qk_norm_eps,
                                     self.position.table(batch), batch.positions, batch.row_req, cache.block_table,
-                                    cache.pool, cache.page_size, self.ctx.status, stored=self.stored)
+                                    cache.pool, cache.page_size, self.ctx.status, stored=self.stored,
+                                    per_head=self.spec.qk_norm == "head")
         elif self.rope_in_product and self.qkv.rope_fuses(T, self.hd):
             # a step of few tokens: rotation and cache append inside the q/k/v product
             q = torch.empty((T, self.qd), dtype=self.ctx.compute_dtype, device=self.ctx.device)
@@ -162,12 +176,14 @@ class GQAAttention:
         out = torch.empty((T, self.nh * kvd_), dtype=self.ctx.compute_dtype, device=q.device)
         ops.attention(q, q.stride(0), cache.pool, cache.block_table, batch.positions, qblk, n_qblk,
                       batch.max_position, T, self.nh, self.nkv, khd, self.window, self.ctx.kv_split, tile, bq,
-                      self.scale, out, self.ctx.status, kernel, vd=kvd_, sink=self.spec.sink)
+                      self.scale, out, self.ctx.status, kernel, vd=kvd_, sink=bool(self.spec.sink),
+                      sink_weight=self.sink_weight, softcap=self.score_cap)
+        gate_per = self.vd if self.spec.gate == "head" else 1      # one gate per head, or one per feature
         if self.spec.gate is not None and self.stored is None:
-            ops.sigmoid_gate(out, qkv, self.gate_col, self.od)
+            ops.sigmoid_gate(out, qkv, self.gate_col, self.od, gate_per=gate_per)
         elif self.spec.gate is not None:               # the gate's kernel also drops the zeros behind every head
             wide, out = out, torch.empty((T, self.od), dtype=self.ctx.compute_dtype, device=q.device)
-            ops.sigmoid_gate(out, qkv, self.gate_col, self.od, src=wide, vd=self.vd, head_stride=self.stored)
+            ops.sigmoid_gate(out, qkv, self.gate_col, self.od, src=wide, vd=self.vd, head_stride=self.stored, gate_per=gate_per)
         elif self.stored is not None:
             out = out.view(T, self.nh, self.stored)[:, :, :self.vd].reshape(T, self.od)
         if stream is None:

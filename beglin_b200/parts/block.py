@@ -11,7 +11,7 @@ import torch
 
 from ..csrc import ops
 from .registry import register_block
-from .stream import NormedInput, ResidualStream
+from .stream import NormedInput, ResidualStream, Terms
 
 
 @register_block("prenorm")
@@ -31,6 +31,7 @@ class PreNormBlock:
         to it); any other part gets the normed rows and returns its addend, which the stream then owes.
         A combiner sees the stream before the sublayers (`begin`) and rewrites it behind them (`forward`)."""
         if self.combiner is not None:
+            stream.settle()
             self.combiner.begin(stream)
         h = NormedInput(stream, self.mixer_norm)
         if getattr(self.mixer, "takes_stream", False):
@@ -83,6 +84,7 @@ class PostNormBlock:
     @staticmethod
     def rows(stream: ResidualStream, dtype: torch.dtype) -> torch.Tensor:
         """The stream's rows in the compute type."""
+        stream.settle()
         if stream.pending is not None:                 # something an earlier block of another kind still owes
             ops.add_residual(stream.x, stream.pending)
             stream.updated(None)
@@ -109,3 +111,58 @@ class PostNormBlock:
 class PostNormMixerBlock(PostNormBlock):
     """The same layer without a feed-forward."""
     SLOTS = (("mixer", "mixer"), ("mixer_norm", "norm"))
+
+
+@register_block("parallel")
+class ParallelBlock:
+    """Both sublayers read the SAME stream, each through a norm of its own, and their sum is added times a constant:
+    x <- x + m (mixer(norm1(x)) + feed_forward(norm2(x))); a layer may lack the feed-forward.  The sum is float.  The
+    block leaves its sublayers' results as terms that the stream still owes, and the next block of this kind adds them
+    in the same kernel that computes its two norms (one pass over the rows for the sum, the statistics and both normed
+    copies); any other reader of the stream has them added first."""
+    SLOTS = (("mixer_norm", "norm"), ("mixer", "mixer"), ("feed_forward_norm", "norm"), ("feed_forward", "feed_forward"))
+
+    def __init__(self, mixer_norm, mixer, feed_forward_norm=None, feed_forward=None, residual_mult: float = 1.0):
+        self.mixer_norm, self.mixer = mixer_norm, mixer
+        self.feed_forward_norm, self.feed_forward = feed_forward_norm, feed_forward
+        self.mult = float(residual_mult)
+
+    def normed(self, stream: ResidualStream):
+        """(norm1(x), norm2(x) or None) of the stream with everything it is owed added."""
+        n1, n2 = self.mixer_norm, self.feed_forward_norm if self.feed_forward is not None else None
+        one_kernel = getattr(n1, "kind", None) == "rmsnorm" and (n2 is None or (
+            getattr(n2, "kind", None) == "rmsnorm" and n2.spec.eps == n1.spec.eps and n2.weight.dtype == n1.weight.dtype))
+        if not one_kernel:
+            stream.settle()
+            h1 = NormedInput(stream, n1).tensor()
+            return h1, (n2.add_norm(stream.x, None) if n2 is not None else None)
+        terms = stream.terms.items if stream.terms is not None else []
+        if stream.pending is not None:
+            terms = [(stream.pending, 1.0)] + list(terms)
+        x, dtype = stream.x, n1.ctx.compute_dtype
+        h1 = torch.empty(x.shape, dtype=dtype, device=x.device)
+        h2 = torch.empty(x.shape, dtype=dtype, device=x.device) if n2 is not None else None
+        ops.add_terms_norm(x, terms, weight1=n1.weight, weight2=n2.weight if n2 is not None else None, eps=n1.spec.eps,
+                           out1=h1, out2=h2)
+        stream.pending, stream.terms, stream.ssq, stream.lowp = None, None, None, None
+        return h1, h2
+
+    def forward(self, stream: ResidualStream, batch, cache) -> None:
+        h1, h2 = self.normed(stream)
+        owed = Terms()
+        if getattr(self.mixer, "takes_stream", False):
+            owed.add(self.mixer.forward(h1, batch, cache, None), self.mult)
+        else:
+            owed.add(self.mixer.forward(h1, batch, cache), self.mult)
+        if self.feed_forward is not None:
+            if getattr(self.feed_forward, "takes_stream", False):
+                owed.add(self.feed_forward.forward(h2, batch, None), self.mult)
+            else:
+                owed.add(self.feed_forward.forward(h2, batch), self.mult)
+        stream.terms = owed
+
+
+@register_block("parallel_mixer")
+class ParallelMixerBlock(ParallelBlock):
+    """The same layer without a feed-forward: x <- x + m mixer(norm1(x))."""
+    SLOTS = (("mixer_norm", "norm"), ("mixer", "mixer"))

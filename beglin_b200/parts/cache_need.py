@@ -51,6 +51,14 @@ class FixedStateNeed:
     dtype: str = "float32"
 
 
+@dataclass(frozen=True)
+class CompositeNeed:
+    """Several needs of one stage, for a mixer made of branches that keep different things (pages of keys and values beside
+    a state of fixed size).  Each joins the group of its own kind; the stage's view is the tuple of their views, with None
+    where a branch keeps nothing."""
+    needs: Tuple[Optional[object], ...]
+
+
 @dataclass
 class PagedKVView:
     """One stage's pages, [num_pages, 2, n_kv_heads, page_size, head_dim] (2 = keys, values) for keys and values

@@ -59,23 +59,26 @@ class SwiGLU:
 
 @register_feed_forward("dense_act")
 class DenseAct:
-    """m = W_down act(W_up h): one hidden layer without a gate branch.  The activation (xIELU) is a kernel of its
-    own between the two products; it reads the up product's result (or its partial sums) as floats and writes
+    """m = W_down act(W_up h): one hidden layer without a gate branch.  The activation (xIELU, the tanh form of GELU or
+    silu) is a kernel of its own between the two products; it reads the up product's result (or its partial sums) as floats and writes
     the compute type."""
 
     @staticmethod
     def expected_tensors(spec: DenseActSpec) -> List[TensorRole]:
-        return [TensorRole("up.weight", (spec.intermediate, spec.hidden), True, True),
-                TensorRole("down.weight", (spec.hidden, spec.intermediate), True, True),
-                TensorRole("act", (2,))]
+        roles = [TensorRole("up.weight", (spec.intermediate, spec.hidden), True, True),
+                 TensorRole("down.weight", (spec.hidden, spec.intermediate), True, True)]
+        if spec.activation == "xielu":
+            roles.append(TensorRole("act", (2,)))
+        return roles
 
     def __init__(self, spec: DenseActSpec, tensors: Dict[str, torch.Tensor], ctx: BuildContext):
-        if spec.activation != "xielu":
-            raise ValueError(f"unknown activation '{spec.activation}' of a dense feed-forward")
+        if spec.activation != "xielu" and spec.activation not in ops.GLU_ACTIVATIONS:
+            raise ValueError(f"unknown activation '{spec.activation}' of a dense feed-forward "
+                             f"(xielu, {', '.join(ops.GLU_ACTIVATIONS)})")
         self.spec, self.ctx = spec, ctx
         self.up = Linear(tensors["up.weight"], None, ctx, label="proj_up")
         self.down = Linear(tensors["down.weight"], None, ctx, label="proj_down")
-        self.act = ctx.vector(tensors["act"])
+        self.act = ctx.vector(tensors["act"]) if spec.activation == "xielu" else None
 
     takes_stream = True        # forward takes a NormedInput and may add its result to the stream itself
 
@@ -86,7 +89,10 @@ class DenseAct:
             h = h.tensor()
         z = self.up.partial(h)
         a = torch.empty((h.shape[0], self.spec.intermediate), dtype=self.ctx.compute_dtype, device=h.device)
-        ops.xielu(z, self.act, a)
+        if self.act is not None:
+            ops.xielu(z, self.act, a)
+        else:
+            ops.activation(z, a, self.spec.activation)
         if stream is None:
             return self.down.partial(a)
         self.down.into(a, stream)

@@ -14,6 +14,7 @@ NORMS: Dict[str, type] = {}
 POSITIONS: Dict[str, type] = {}
 BLOCKS: Dict[str, type] = {}
 COMBINERS: Dict[str, type] = {}      # what a block does to the stream behind its sublayers (depth averages)
+ENTRIES: Dict[str, type] = {}        # what rewrites the stream in front of a stage (the input of a pass of a loop)
 
 
 def _register(table: Dict[str, type], what: str) -> Callable[[str], Callable[[type], type]]:
@@ -32,6 +33,7 @@ register_norm = _register(NORMS, "norm")
 register_position = _register(POSITIONS, "position encoding")
 register_block = _register(BLOCKS, "block")
 register_combiner = _register(COMBINERS, "combiner")
+register_entry = _register(ENTRIES, "entry")
 
 
 def lookup(table: Dict[str, type], kind: str, what: str) -> type:
@@ -56,6 +58,10 @@ def norm_class(kind: str) -> type:
 
 def position_class(kind: str) -> type:
     return lookup(POSITIONS, kind, "position encoding")
+
+
+def entry_class(kind: str) -> type:
+    return lookup(ENTRIES, kind, "entry")
 
 
 def block_class(kind: str) -> type:

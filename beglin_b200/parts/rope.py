@@ -1,7 +1,8 @@
 """Rotary position encoding.  Frequency i is theta^(-2i/rot) * scale_i; the angle of a token is its
 position times the frequency, as a float product, and its cosine and sine are computed once per
 step for all layers and heads (qwen_infer.c:757-794).  The table is made by the `rope_table`
-kernel; the rotation itself is fused into the cache append (`rope_kv_append`).
+kernel; the rotation itself is fused into the cache append (`rope_kv_append`).  A spec may give the
+frequencies outright (an architecture that stretches and blends them) and an amplitude on cosine and sine.
 
 The frequencies are 32-bit numbers made the way the reference makes them (qwen_infer.c:791):
 `powf(theta, -(2.0f*i)/hd)` of the 32-bit theta and the 32-bit exponent, times the 32-bit scale.
@@ -40,6 +41,12 @@ class RotaryPosition:
             if len(spec.freq_scale) != half:
                 raise ValueError("freq_scale must have rotary_dim/2 entries")
             inv = inv * np.asarray(spec.freq_scale, dtype=np.float32)
+        if spec.frequencies is not None:
+            # the frequencies themselves, worked out in 64-bit by the architecture (stretched, blended): rounded once
+            if len(spec.frequencies) != half:
+                raise ValueError("frequencies must have rotary_dim/2 entries")
+            inv = np.asarray(spec.frequencies, dtype=np.float64).astype(np.float32)
+        self.amplitude = float(np.float32(spec.amplitude))
         self.inv_freq = torch.from_numpy(inv.astype(np.float32)).to(ctx.device)
         self.rotary_dim = spec.rotary_dim
         self.interleaved = spec.pairing == "interleaved"
@@ -50,7 +57,7 @@ class RotaryPosition:
         t = batch.scratch.get(key)
         if t is None:
             t = torch.empty((batch.n_rows, self.rotary_dim // 2, 2), dtype=torch.float32, device=self.ctx.device)
-            ops.rope_table(batch.positions, self.inv_freq, t)
+            ops.rope_table(batch.positions, self.inv_freq, t, self.amplitude)
             batch.scratch[key] = t
         return t
 

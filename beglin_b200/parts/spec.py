@@ -45,13 +45,17 @@ class PositionSpec:
     (i, i + rotary_dim/2) for pairing "split_half" (qwen_infer.c:782-790) or (2i, 2i+1) for
     "interleaved" (qwen_infer.c:738-750); frequency i is theta^(-2i/rotary_dim) * freq_scale[i]
     (qwen_infer.c:757-794).  kind "none" rotates nothing.  `freq_divisor` d divides every frequency (positions
-    stretched d times, "linear scaling"); with it the frequencies are worked out in 64-bit and rounded once."""
+    stretched d times, "linear scaling"); with it the frequencies are worked out in 64-bit and rounded once.
+    `frequencies`, when given, ARE the rotary_dim/2 frequencies (worked out by whoever wrote the spec, in 64-bit; rounded
+    once here), and theta, freq_scale and freq_divisor play no part.  `amplitude` multiplies every cosine and sine."""
     kind: str = "rope"
     rotary_dim: int = 0
     theta: float = 10000.0
     pairing: str = "split_half"
     freq_scale: Optional[Tuple[float, ...]] = None
     freq_divisor: Optional[float] = None
+    frequencies: Optional[Tuple[float, ...]] = None
+    amplitude: float = 1.0
 
 
 @dataclass(frozen=True)
@@ -65,7 +69,11 @@ class AttentionSpec:
     query row and the whole key row of a token (all heads at once) are RMS-normed with weights of their own,
     before the rotation, with `qk_norm_eps`.  `sink`: the softmax's denominator is enlarged by one, as if every
     query saw one more key of score 0 that carries no value.  `gate` "elementwise": the joined heads are multiplied
-    by sigmoid of a further product of the mixer's input, feature by feature, before the output product."""
+    by sigmoid of a further product of the mixer's input, feature by feature, before the output product; `gate` "head": that
+    product gives ONE number per query head, whose sigmoid multiplies the head's result.  `qk_norm` "head": every head of
+    the queries and of the keys is RMS-normed by itself, with one weight vector of head_dim values for all query heads and one
+    for all key heads.  `sink` "learned": the extra key's score is a learned number per query head (tensor `sink`) in place
+    of 0.  `score_cap` c: a scaled score s becomes c tanh(s / c) before the softmax."""
     hidden: int
     n_heads: int
     n_kv_heads: int
@@ -77,10 +85,11 @@ class AttentionSpec:
     scale: Optional[float] = None          # None: 1/sqrt(head_dim)  (qwen_infer.c:1488)
     own_kv: bool = True
     v_head_dim: Optional[int] = None       # None: head_dim
-    qk_norm: Optional[str] = None          # None or "projection"
+    qk_norm: Optional[str] = None          # None, "projection" or "head"
     qk_norm_eps: float = 0.0
-    sink: bool = False
-    gate: Optional[str] = None             # None or "elementwise"
+    sink: object = False                   # False, True (a key of score 0) or "learned" (a score per query head)
+    gate: Optional[str] = None             # None, "elementwise" or "head"
+    score_cap: Optional[float] = None      # None: scores as they are
     kind: str = "gqa_attention"
 
     @property
@@ -155,9 +164,45 @@ class Mamba2Spec:
 
 
 @dataclass(frozen=True)
+class DecayAttentionSpec:
+    """Linear attention with a constant decay per head: `n_heads` heads with queries and keys of `dim` features and values
+    of `vdim`; q, k, v = silu of products of the mixer's input; per head a state S <- decay_h S + k v^T [dim, vdim] that
+    is read out as S^T q.  The joined heads are RMS-normed together with a weight (`eps`), multiplied feature by feature by
+    sigmoid of a further product of the input, and projected."""
+    hidden: int
+    n_heads: int
+    dim: int
+    vdim: int
+    decay: Tuple[float, ...]
+    eps: float
+    kind: str = "decay_attention"
+
+
+@dataclass(frozen=True)
+class ParallelMixersSpec:
+    """Several mixers side by side that read the same input; the result is sum_i scales[i] * mixer_i(h).  `labels` name the
+    branches: branch i's tensors are called `<labels[i]>.<the mixer's own name>`.  Every branch has a cache of its own
+    kind (pages, state) or none."""
+    hidden: int
+    branches: Tuple[object, ...]
+    scales: Tuple[float, ...]
+    labels: Tuple[str, ...]
+    kind: str = "parallel_mixers"
+
+
+@dataclass(frozen=True)
+class InputMixSpec:
+    """What stands in front of a stage: the stream is replaced by W [x; e], e the embedded rows of the step and W
+    [hidden, 2 hidden] (the stream's half first)."""
+    hidden: int
+    kind: str = "input_mix"
+
+
+@dataclass(frozen=True)
 class DenseActSpec:
     """Feed-forward with one hidden layer, down(act(up(h))), no gate branch.  `activation` "xielu": a parabola
-    above zero and a scaled exponential below, with two learned numbers."""
+    above zero and a scaled exponential below, with two learned numbers (tensor `act`); "gelu_tanh" and "silu" have no
+    tensor of their own."""
     hidden: int
     intermediate: int
     activation: str = "xielu"
@@ -182,15 +227,17 @@ class LayerSpec:
 
     The slots may also be given as keywords (`LayerSpec(mixer=..., feed_forward=..., names=...)`) and
     read as attributes (`layer.mixer`); `with_parts` returns a copy with some slots, the names or the
-    block kind replaced."""
+    block kind replaced.  `block_args` are the constants of the block kind itself (keyword arguments of its class, e.g. the
+    factor on the sublayers' sum of a "parallel" block)."""
 
     def __init__(self, parts: Optional[Dict[str, object]] = None, names: Optional[Dict[str, str]] = None,
-                 block: str = "prenorm", **slots):
+                 block: str = "prenorm", block_args: Optional[Dict[str, object]] = None, **slots):
         merged = dict(parts or {})
         merged.update(slots)
         object.__setattr__(self, "parts", merged)
         object.__setattr__(self, "names", dict(names or {}))
         object.__setattr__(self, "block", block)
+        object.__setattr__(self, "block_args", dict(block_args or {}))
 
     def __getattr__(self, slot):
         parts = self.__dict__.get("parts", {})
@@ -204,7 +251,8 @@ class LayerSpec:
     def with_parts(self, names: Optional[Dict[str, str]] = None, block: Optional[str] = None, **slots) -> "LayerSpec":
         parts = dict(self.parts)
         parts.update(slots)
-        return LayerSpec(parts, self.names if names is None else names, self.block if block is None else block)
+        return LayerSpec(parts, self.names if names is None else names, self.block if block is None else block,
+                         self.block_args)
 
     def __repr__(self):
         return f"LayerSpec(block={self.block!r}, parts={self.parts!r})"
@@ -213,9 +261,18 @@ class LayerSpec:
 @dataclass(frozen=True)
 class Stage:
     """One entry of the run order: which layer runs, and whose cache it uses.  `cache` None means
-    a cache of its own; a number names an earlier stage of the order whose cache is read."""
+    a cache of its own; a number names an earlier stage of the order whose cache is read.  `enter` names one of the
+    model's `entries`, a part that rewrites the stream right before this stage runs."""
     layer: int
     cache: Optional[int] = None
+    enter: Optional[int] = None
+
+
+@dataclass(eq=False)
+class EntrySpec:
+    """A part in front of stages (family "entry"): its spec and the checkpoint names of its tensors."""
+    part: object
+    names: Dict[str, str]
 
 
 @dataclass
@@ -234,3 +291,4 @@ class ModelSpec:
     logit_softcap: float = 0.0            # c > 0: logits = c * tanh(logits / c)
     eos_ids: Tuple[int, ...] = ()
     extra: Dict[str, object] = field(default_factory=dict)
+    entries: List[EntrySpec] = field(default_factory=list)   # parts that stages name in `enter`

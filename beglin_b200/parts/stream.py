@@ -15,6 +15,22 @@ from typing import Optional
 import torch
 
 
+class Terms:
+    """Results that are to be added to the stream, each times a constant: [(tensor or partial sums, constant), ...]."""
+
+    def __init__(self, items=None):
+        self.items = list(items or [])
+
+    def add(self, tensor, scale: float = 1.0) -> None:
+        if isinstance(tensor, Terms):
+            self.items += [(t, c * scale) for t, c in tensor.items]
+        elif tensor is not None:
+            self.items.append((tensor, float(scale)))
+
+    def scaled(self, scale: float) -> "Terms":
+        return Terms([(t, c * scale) for t, c in self.items])
+
+
 class ResidualStream:
     def __init__(self, x: torch.Tensor):
         self.x = x                                     # float32 [T, d]
@@ -24,6 +40,17 @@ class ResidualStream:
         #                                                results so far, kept by a combiner that mixes over depth
         self.lowp: Optional[torch.Tensor] = None       # x's rows in the compute type, as the kernel that last changed
         #                                                x left them (for sublayers that read the stream un-normed)
+        self.terms: Optional[Terms] = None             # not yet added to x either: results with constants of their own
+        #                                                (a block that adds scaled sums; whoever reads x calls settle())
+        self.origin: Optional[torch.Tensor] = None     # float32 [T, d]: the embedded rows, kept for parts that mix them in
+
+    def settle(self) -> None:
+        """Adds the scaled terms that are still owed to x (the blocks that leave such terms fold the sum into their own
+        next kernel; every other reader of x calls this first)."""
+        if self.terms is not None:
+            from ..csrc import ops
+            ops.add_terms_norm(self.x, self.terms.items)
+            self.terms, self.ssq, self.lowp = None, None, None
 
     def owe(self, addend: torch.Tensor) -> None:
         self.pending, self.ssq, self.lowp = addend, None, None
@@ -48,6 +75,7 @@ class NormedInput:
     def tensor(self) -> torch.Tensor:
         if self._tensor is None:
             s = self.stream
+            s.settle()
             had = s.pending is not None
             self._tensor = self.norm.add_norm(s.x, s.pending)
             s.pending = None
@@ -58,6 +86,6 @@ class NormedInput:
     def fusable(self):
         """(weight, eps) of the norm when a product may apply it to the stream itself, else None."""
         s = self.stream
-        if self._tensor is not None or s.pending is not None or s.ssq is None:
+        if self._tensor is not None or s.pending is not None or s.terms is not None or s.ssq is None:
             return None
         return getattr(self.norm, "fusion", lambda: None)()

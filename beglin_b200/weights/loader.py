@@ -53,6 +53,11 @@ def expected_tensors(spec: ModelSpec) -> Dict[str, TensorRole]:
             if qualified not in layer.names:
                 raise KeyError(f"layer {li}: the name map has no checkpoint name for '{qualified}'")
             out[layer.names[qualified]] = role
+    for ei, entry in enumerate(getattr(spec, "entries", ())):
+        for role in registry.entry_class(entry.part.kind).expected_tensors(entry.part):
+            if role.name not in entry.names:
+                raise KeyError(f"entry {ei}: the name map has no checkpoint name for '{role.name}'")
+            out[entry.names[role.name]] = role
     norm_cls = registry.norm_class(spec.final_norm.kind)
     for role in norm_cls.expected_tensors(spec.final_norm):
         # a norm has one tensor, "weight"; the final norm's checkpoint name is given whole
