@@ -53,12 +53,19 @@ struct AttnMmaParams {
     int nh, nkv, group;
     int window, split;
     float scale_log2;       // scale * log2(e)
+    float cap_log2;         // c * log2(e) when scores are squashed to c tanh(score / c), else 0
+    float scale_over_cap;   // scale / c
     unsigned* status;
     __nv_bfloat16* out;     // rows arrangement only: when set, a CTA walks ALL keys of its block and writes
     int out_stride;         // the finished rows here (no partial results, no merge)
     int use_tma;            // pages are copied as TMA boxes (the page size divides 64)
     int whole_pages;        // a page is a stage (64 positions): keys and values of a stage come in ONE box
 };
+
+// A product q . k as the exponent of two that the softmax takes: scaled, squashed when the layer asks for it.
+__device__ __forceinline__ float am_score(float c, const AttnMmaParams& p) {
+    return p.cap_log2 > 0.0f ? p.cap_log2 * tanhf(c * p.scale_over_cap) : c * p.scale_log2;
+}
 
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
     unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
@@ -446,7 +453,7 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_co
                 for (int e = 0; e < 4; ++e) {
                     const int key = w_key0 + kb * 16 + (lane >> 2) + 8 * (e >> 1);
                     const bool ok = all_seen || (key <= pos && key >= lo && key >= k_begin && key < k_end);
-                    const float v = (ok && r0 + (e & 1) < n_rows) ? c[kb][e] * p.scale_log2 : -INFINITY;
+                    const float v = (ok && r0 + (e & 1) < n_rows) ? am_score(c[kb][e], p) : -INFINITY;
                     c[kb][e] = v;
                     tmax[e & 1] = fmaxf(tmax[e & 1], v);
                 }
@@ -518,7 +525,7 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_co
                 for (int j = 0; j < 2 * KB; ++j)
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        sc[j][e] *= p.scale_log2;
+                        sc[j][e] = am_score(sc[j][e], p);
                         tmax[e >> 1] = fmaxf(tmax[e >> 1], sc[j][e]);
                     }
             } else {
@@ -529,7 +536,7 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_co
                         const int key = w_key0 + j * 8 + (lane & 3) * 2 + (e & 1);
                         const int h = e >> 1;
                         const bool ok = key <= pos_r[h] && key >= lo_r[h] && key >= k_begin && key < k_end;
-                        const float v = ok ? sc[j][e] * p.scale_log2 : -INFINITY;
+                        const float v = ok ? am_score(sc[j][e], p) : -INFINITY;
                         sc[j][e] = v;
                         tmax[h] = fmaxf(tmax[h], v);
                     }
@@ -730,7 +737,7 @@ extern "C" int bg_attention_mma_partial(const void* q, int q_stride, const void*
                                         const int* block_table, int max_pages, const int* positions, const int* qblk,
                                         int n_qblk, float* part_o, float* part_ml, int max_splits, int n_splits_launch,
                                         int nh, int nkv, int hd, int window, int split, int by_keys, float scale,
-                                        void* direct_out, int out_stride, unsigned* status, cudaStream_t stream) {
+                                        float softcap, void* direct_out, int out_stride, unsigned* status, cudaStream_t stream) {
     if (n_qblk <= 0 || n_splits_launch <= 0) return BG_OK;
     if (direct_out && (n_splits_launch != 1 || (out_stride % 2) != 0)) return BG_ERR_SHAPE;
     if (nh % nkv != 0 || split % AM_STAGE_KEYS != 0 || (split <= 0 && !by_keys)) return BG_ERR_SHAPE;
@@ -744,6 +751,7 @@ extern "C" int bg_attention_mma_partial(const void* q, int q_stride, const void*
     p.positions = positions; p.qblk = qblk; p.part_o = part_o; p.part_ml = part_ml; p.max_splits = max_splits;
     p.nh = nh; p.nkv = nkv; p.group = nh / nkv; p.window = window; p.split = split;
     p.scale_log2 = scale * AM_LOG2E; p.status = status;
+    p.cap_log2 = softcap > 0.0f ? softcap * AM_LOG2E : 0.0f; p.scale_over_cap = softcap > 0.0f ? scale / softcap : 0.0f;
     p.out = (__nv_bfloat16*)direct_out; p.out_stride = out_stride;
     if (by_keys ? p.group > 16 : p.group > 64) return BG_ERR_UNSUPPORTED;
     if (hd != 64 && hd != 128) return BG_ERR_UNSUPPORTED;

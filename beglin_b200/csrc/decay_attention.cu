@@ -83,6 +83,212 @@ __global__ void __launch_bounds__(256) decay_attention_seq_kernel(DecayAttnParam
 }
 
 // ---------------------------------------------------------------------------------------------------------------
+// Long portions in chunks of DC tokens.  With S the state at a chunk's start, r its number of tokens and t, j = 0 .. r-1:
+//     o_t     = d^(t+1) S^T q_t + sum_{j <= t} d^(t-j) (q_t . k_j) v_j
+//     S_next  = d^r S + A,    A = sum_j d^(r-1-j) k_j v_j^T
+// decay_chunk_sum_kernel    A of every chunk (a block per head and chunk)
+// decay_chunk_scan_kernel   a thread per element of the state walks its request's chunks: A is replaced by the state at
+//                           the chunk's start, the request's slot gets the state behind its last chunk
+// decay_chunk_out_kernel    o of every chunk (a block per head and chunk): scores of the chunk's own tokens times their
+//                           powers of d, then both sums
+// Powers of d come from one table made by repeated multiplication, so d = 0 and d = 1 need no logarithm.  Threads own
+// 4 x 4 tiles of outputs; rows of shared memory are padded to multiples of four floats and read as float4.
+constexpr int DC = 64;                    // tokens of a chunk
+constexpr int DCP = DC + 4;               // row stride of the transposed tiles [feature][token]
+
+struct DecayChunkParams {
+    const void* src; int src_stride; int parts; size_t part_stride;
+    int q_col, k_col, v_col;
+    const float* decay;
+    float* state; size_t slot_stride; const int* slots;
+    const int* chunks;                    // [n_chunks][4] = (request, first row, rows, -)
+    const int* longs;                     // [n_long][4]   = (request, first row, rows, first chunk)
+    float* work;                          // [n_chunks][H][n * nv]
+    float* y;
+    int H, n, nv, np, nvp;                // np, nvp: n, nv rounded up to multiples of 4
+};
+
+__device__ __forceinline__ void decay_powers(float* pw, float d) {      // pw[k] = d^k, k = 0 .. DC
+    if (threadIdx.x == 0) {
+        float v = 1.0f;
+        for (int k = 0; k <= DC; ++k) { pw[k] = v; v *= d; }
+    }
+}
+
+#define DA_FMA44(acc, a, b)                                                                                      \
+    do {                                                                                                         \
+        acc[0][0] = fmaf(a.x, b.x, acc[0][0]); acc[0][1] = fmaf(a.x, b.y, acc[0][1]); acc[0][2] = fmaf(a.x, b.z, acc[0][2]); acc[0][3] = fmaf(a.x, b.w, acc[0][3]); \
+        acc[1][0] = fmaf(a.y, b.x, acc[1][0]); acc[1][1] = fmaf(a.y, b.y, acc[1][1]); acc[1][2] = fmaf(a.y, b.z, acc[1][2]); acc[1][3] = fmaf(a.y, b.w, acc[1][3]); \
+        acc[2][0] = fmaf(a.z, b.x, acc[2][0]); acc[2][1] = fmaf(a.z, b.y, acc[2][1]); acc[2][2] = fmaf(a.z, b.z, acc[2][2]); acc[2][3] = fmaf(a.z, b.w, acc[2][3]); \
+        acc[3][0] = fmaf(a.w, b.x, acc[3][0]); acc[3][1] = fmaf(a.w, b.y, acc[3][1]); acc[3][2] = fmaf(a.w, b.z, acc[3][2]); acc[3][3] = fmaf(a.w, b.w, acc[3][3]); \
+    } while (0)
+
+template <typename TS>
+__global__ void __launch_bounds__(256) decay_chunk_sum_kernel(DecayChunkParams p) {
+    extern __shared__ __align__(16) float dc_s[];
+    const int n = p.n, nv = p.nv, np = p.np, nvp = p.nvp;
+    float* Ks = dc_s;                          // [DC][np], k_j times d^(r-1-j)
+    float* Vs = Ks + (size_t)DC * np;          // [DC][nvp]
+    float* pw = Vs + (size_t)DC * nvp;         // [DC + 1]
+    pdl_launch();
+    const int h = blockIdx.x, c = blockIdx.y, tid = threadIdx.x;
+    decay_powers(pw, p.decay[h]);
+    pdl_wait();
+    const int row0 = p.chunks[c * 4 + 1], rows = p.chunks[c * 4 + 2];
+    __syncthreads();
+    const TS* src = (const TS*)p.src;
+    for (int idx = tid; idx < DC * np; idx += blockDim.x) {
+        const int j = idx / np, i = idx - j * np;
+        float v = 0.0f;
+        if (j < rows && i < n)
+            v = da_silu(sum_parts(src + (size_t)(row0 + j) * p.src_stride + p.k_col + h * n + i, p.parts, p.part_stride)) * pw[rows - 1 - j];
+        Ks[idx] = v;
+    }
+    for (int idx = tid; idx < DC * nvp; idx += blockDim.x) {
+        const int j = idx / nvp, i = idx - j * nvp;
+        float v = 0.0f;
+        if (j < rows && i < nv)
+            v = da_silu(sum_parts(src + (size_t)(row0 + j) * p.src_stride + p.v_col + h * nv + i, p.parts, p.part_stride));
+        Vs[idx] = v;
+    }
+    __syncthreads();
+    float* A = p.work + ((size_t)c * p.H + h) * n * nv;
+    const int tc = nvp / 4, tiles = (np / 4) * tc;
+    for (int tile = tid; tile < tiles; tile += blockDim.x) {
+        const int i0 = (tile / tc) * 4, c0 = (tile % tc) * 4;
+        float acc[4][4] = {};
+        for (int j = 0; j < rows; ++j) {
+            const float4 kk = *(const float4*)(Ks + (size_t)j * np + i0);
+            const float4 vv = *(const float4*)(Vs + (size_t)j * nvp + c0);
+            DA_FMA44(acc, kk, vv);
+        }
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+            for (int b = 0; b < 4; ++b)
+                if (i0 + a < n && c0 + b < nv) A[(size_t)(i0 + a) * nv + c0 + b] = acc[a][b];
+    }
+}
+
+__global__ void __launch_bounds__(256) decay_chunk_scan_kernel(DecayChunkParams p) {
+    pdl_launch();
+    pdl_wait();
+    const int e = blockIdx.x * blockDim.x + threadIdx.x, h = blockIdx.y, l = blockIdx.z;
+    const int sz = p.n * p.nv;
+    if (e >= sz) return;
+    const int req = p.longs[l * 4 + 0], rows = p.longs[l * 4 + 2], c0 = p.longs[l * 4 + 3];
+    const float d = p.decay[h];
+    float dfull = 1.0f;
+    for (int k = 0; k < DC; ++k) dfull *= d;
+    float* st = p.state + (size_t)p.slots[req] * p.slot_stride + (size_t)h * sz + e;
+    float S = *st;
+    for (int c = 0, left = rows; left > 0; ++c, left -= DC) {
+        float dr = dfull;
+        if (left < DC) { dr = 1.0f; for (int k = 0; k < left; ++k) dr *= d; }
+        float* a = p.work + ((size_t)(c0 + c) * p.H + h) * sz + e;
+        const float A = *a;
+        *a = S;
+        S = fmaf(dr, S, A);
+    }
+    *st = S;
+}
+
+template <typename TS>
+__global__ void __launch_bounds__(256) decay_chunk_out_kernel(DecayChunkParams p) {
+    extern __shared__ __align__(16) float dc_s[];
+    const int n = p.n, nv = p.nv, np = p.np, nvp = p.nvp;
+    float* Qt = dc_s;                          // [np][DCP]
+    float* Kt = Qt + (size_t)np * DCP;         // [np][DCP]
+    float* Vs = Kt + (size_t)np * DCP;         // [DC][nvp]
+    float* Ss = Vs + (size_t)DC * nvp;         // [np][nvp]
+    float* Pt = Ss + (size_t)np * nvp;         // [DC (key)][DCP (query)]
+    float* pw = Pt + (size_t)DC * DCP;         // [DC + 1]
+    pdl_launch();
+    const int h = blockIdx.x, c = blockIdx.y, tid = threadIdx.x;
+    decay_powers(pw, p.decay[h]);
+    pdl_wait();
+    const int row0 = p.chunks[c * 4 + 1], rows = p.chunks[c * 4 + 2];
+    const TS* src = (const TS*)p.src;
+    for (int idx = tid; idx < DC * np; idx += blockDim.x) {
+        const int j = idx / np, i = idx - j * np;
+        float q = 0.0f, k = 0.0f;
+        if (j < rows && i < n) {
+            const TS* row = src + (size_t)(row0 + j) * p.src_stride + h * n + i;
+            q = da_silu(sum_parts(row + p.q_col, p.parts, p.part_stride));
+            k = da_silu(sum_parts(row + p.k_col, p.parts, p.part_stride));
+        }
+        Qt[(size_t)i * DCP + j] = q;
+        Kt[(size_t)i * DCP + j] = k;
+    }
+    for (int idx = tid; idx < DC * nvp; idx += blockDim.x) {
+        const int j = idx / nvp, i = idx - j * nvp;
+        float v = 0.0f;
+        if (j < rows && i < nv)
+            v = da_silu(sum_parts(src + (size_t)(row0 + j) * p.src_stride + p.v_col + h * nv + i, p.parts, p.part_stride));
+        Vs[idx] = v;
+    }
+    const float* S0 = p.work + ((size_t)c * p.H + h) * n * nv;
+    for (int idx = tid; idx < np * nvp; idx += blockDim.x) {
+        const int i = idx / nvp, cc = idx - i * nvp;
+        Ss[idx] = (i < n && cc < nv) ? S0[(size_t)i * nv + cc] : 0.0f;
+    }
+    __syncthreads();
+    // scores of the chunk's own tokens: a 4 x 4 tile (queries t0.., keys j0..) per thread
+    for (int tile = tid; tile < (DC / 4) * (DC / 4); tile += blockDim.x) {
+        const int t0 = (tile / (DC / 4)) * 4, j0 = (tile % (DC / 4)) * 4;
+        float acc[4][4] = {};
+        if (j0 <= t0 + 3 && j0 < rows && t0 < rows) {
+            for (int i = 0; i < n; ++i) {
+                const float4 qq = *(const float4*)(Qt + (size_t)i * DCP + t0);
+                const float4 kk = *(const float4*)(Kt + (size_t)i * DCP + j0);
+                DA_FMA44(acc, qq, kk);
+            }
+        }
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                const int t = t0 + a, j = j0 + b;
+                Pt[(size_t)j * DCP + t] = j <= t ? acc[a][b] * pw[t - j] : 0.0f;
+            }
+    }
+    __syncthreads();
+    const int tc = nvp / 4, tiles = (DC / 4) * tc;
+    for (int tile = tid; tile < tiles; tile += blockDim.x) {
+        const int t0 = (tile / tc) * 4, c0 = (tile % tc) * 4;
+        if (t0 >= rows) continue;
+        float acc[4][4] = {};
+        for (int i = 0; i < n; ++i) {
+            const float4 qq = *(const float4*)(Qt + (size_t)i * DCP + t0);
+            const float4 ss = *(const float4*)(Ss + (size_t)i * nvp + c0);
+            DA_FMA44(acc, qq, ss);
+        }
+#pragma unroll
+        for (int a = 0; a < 4; ++a) {
+            const float w = pw[t0 + a + 1];
+#pragma unroll
+            for (int b = 0; b < 4; ++b) acc[a][b] *= w;
+        }
+        const int jend = min(rows, t0 + 4);
+        for (int j = 0; j < jend; ++j) {
+            const float4 pp = *(const float4*)(Pt + (size_t)j * DCP + t0);
+            const float4 vv = *(const float4*)(Vs + (size_t)j * nvp + c0);
+            DA_FMA44(acc, pp, vv);
+        }
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+            for (int b = 0; b < 4; ++b)
+                if (t0 + a < rows && c0 + b < nv)
+                    p.y[(size_t)(row0 + t0 + a) * p.H * nv + (size_t)h * nv + c0 + b] = acc[a][b];
+    }
+}
+
+static size_t decay_chunk_out_smem(int np, int nvp) {
+    return ((size_t)2 * np * DCP + (size_t)DC * nvp + (size_t)np * nvp + (size_t)DC * DCP + DC + 4) * sizeof(float);
+}
+
+// ---------------------------------------------------------------------------------------------------------------
 // x[t] (= or +=) sum_i scale_i * term_i[t], term_i a [T, d] tensor of either type or the float partial sums of a
 // split product; then, when asked, the rows of x RMS-normed with one or two weight vectors (the two norms of a layer
 // whose sublayers read the same stream share the statistics).  The sum and the statistics are float.
@@ -156,6 +362,51 @@ extern "C" int bg_decay_attention(const void* src, int src_dtype, int src_stride
             if (e != cudaSuccess) return (int)e;
         }
         launch(kern, dim3(H, n_req), dim3(threads), smem, stream, p);
+    });
+    BG_LAUNCH_CHECK();
+    return BG_OK;
+}
+
+// 0 when the chunked kernels take heads of n x nv values (their tiles fit in shared memory), else BG_ERR_UNSUPPORTED.
+extern "C" int bg_decay_attention_chunk_plan(int n, int nv, int* chunk) {
+    if (n <= 0 || nv <= 0) return BG_ERR_SHAPE;
+    const int np = (n + 3) / 4 * 4, nvp = (nv + 3) / 4 * 4;
+    if (chunk) *chunk = DC;
+    return decay_chunk_out_smem(np, nvp) <= 200 * 1024 ? BG_OK : BG_ERR_UNSUPPORTED;
+}
+
+// The chunked form for requests of many rows.  chunks [n_chunks][4] = (request, first row, rows <= chunk, -) lists every
+// long request's chunks in turn; longs [n_long][4] = (request, first row, rows, index of its first chunk); work is
+// float [n_chunks][H][n * nv].
+extern "C" int bg_decay_attention_chunked(const void* src, int src_dtype, int src_stride, int parts, long long part_stride,
+                                          int q_col, int k_col, int v_col, const float* decay, float* state, long long slot_stride,
+                                          const int* slots, const int* chunks, int n_chunks, const int* longs, int n_long,
+                                          float* work, float* y, int H, int n, int nv, cudaStream_t stream) {
+    if (n_chunks <= 0 || n_long <= 0) return BG_OK;
+    if (H <= 0 || n <= 0 || nv <= 0 || parts < 1 || n_chunks > 65535 || n_long > 65535 || H > 65535) return BG_ERR_SHAPE;
+    DecayChunkParams p;
+    p.src = src; p.src_stride = src_stride; p.parts = parts; p.part_stride = (size_t)part_stride; p.q_col = q_col; p.k_col = k_col;
+    p.v_col = v_col; p.decay = decay; p.state = state; p.slot_stride = (size_t)slot_stride; p.slots = slots; p.chunks = chunks;
+    p.longs = longs; p.work = work; p.y = y; p.H = H; p.n = n; p.nv = nv; p.np = (n + 3) / 4 * 4; p.nvp = (nv + 3) / 4 * 4;
+    const size_t smem_sum = ((size_t)DC * p.np + (size_t)DC * p.nvp + DC + 4) * sizeof(float);
+    const size_t smem_out = decay_chunk_out_smem(p.np, p.nvp);
+    if (smem_out > 200 * 1024 || smem_sum > 200 * 1024) return BG_ERR_UNSUPPORTED;
+    BG_DISPATCH_DTYPE(src_dtype, TS, {
+        auto ksum = decay_chunk_sum_kernel<TS>;
+        auto kout = decay_chunk_out_kernel<TS>;
+        if (smem_sum > BG_SMEM_OPT_IN) {
+            cudaError_t e = cudaFuncSetAttribute(ksum, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_sum);
+            if (e != cudaSuccess) return (int)e;
+        }
+        if (smem_out > BG_SMEM_OPT_IN) {
+            cudaError_t e = cudaFuncSetAttribute(kout, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_out);
+            if (e != cudaSuccess) return (int)e;
+        }
+        launch(ksum, dim3(H, n_chunks), dim3(256), smem_sum, stream, p);
+        BG_LAUNCH_CHECK();
+        launch(decay_chunk_scan_kernel, dim3((n * nv + 255) / 256, H, n_long), dim3(256), 0, stream, p);
+        BG_LAUNCH_CHECK();
+        launch(kout, dim3(H, n_chunks), dim3(256), smem_out, stream, p);
     });
     BG_LAUNCH_CHECK();
     return BG_OK;

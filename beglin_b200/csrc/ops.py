@@ -62,12 +62,16 @@ _SIGNATURES = {
                         _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "bg_decay_attention": [_c_void_p, _c_int, _c_int, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_ll, _c_void_p,
                            _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
+    "bg_decay_attention_chunk_plan": [_c_int, _c_int, ctypes.POINTER(_c_int)],
+    "bg_decay_attention_chunked": [_c_void_p, _c_int, _c_int, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_ll,
+                                   _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int,
+                                   _c_void_p],
     "bg_add_terms_norm": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                           _c_void_p, _c_void_p, _c_int, _c_float, _c_void_p, _c_void_p, _c_int, _c_void_p],
     "bg_attention_mma_plan": [_c_int, _c_int, _c_int, ctypes.POINTER(_c_int)],
     "bg_attention_mma_partial": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p,
                                  _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
-                                 _c_int, _c_float, _c_void_p, _c_int, _c_void_p, _c_void_p],
+                                 _c_int, _c_float, _c_float, _c_void_p, _c_int, _c_void_p, _c_void_p],
     "bg_attention_tc_plan": [_c_int, _c_int, _c_int, ctypes.POINTER(_c_int)],
     "bg_attention_tc": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int,
                         _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void_p, _c_void_p],
@@ -474,7 +478,8 @@ def attention_wide_from(keys: int = 0) -> int:
 
 
 TC_ROWS_FOR = ("auto", "tcgen05")
-TC_OPTIONS = ()                                # options of the softmax that the tensor-core kernels know besides the plain one
+TC_OPTIONS = ()                                # options of the softmax that the tcgen05 kernel knows besides the plain one
+MMA_OPTIONS = ("softcap", "sink_weight")       # ... and the mma kernels (the sink's share is added where partial results merge)
 SINK_KERNELS = ("generic", "tc_rows", "mma_keys", "mma_rows")   # every kernel can take the enlarged denominator (`sink`)
 
 
@@ -488,13 +493,14 @@ def attention_plan(group: int, hd: int, dtype: torch.dtype = torch.float32, deco
     if prefer not in ("auto", "generic", "mma", "tcgen05"):
         raise KernelError(f"unknown attention kernel choice '{prefer}'")
     vd = hd if vd is None else vd
-    if softcap and "softcap" not in TC_OPTIONS:
-        prefer = "generic"                     # squashed scores are known to the CUDA-core kernel only
+    tc_knows = (not softcap or "softcap" in TC_OPTIONS) and (not learned_sink or "sink_weight" in TC_OPTIONS)
+    if prefer == "tcgen05" and not tc_knows:
+        raise KernelError("the tcgen05 attention kernel knows neither squashed scores nor a learned sink")
     if vd != hd:
         if prefer in ("mma", "tcgen05"):
             raise KernelError(f"the tensor-core attention kernels take values of the keys' size ({hd}), not {vd}")
         prefer = "generic"
-    if dtype == torch.bfloat16 and not decode_only and prefer in TC_ROWS_FOR and (not learned_sink or "sink_weight" in TC_OPTIONS):
+    if dtype == torch.bfloat16 and not decode_only and prefer in TC_ROWS_FOR and tc_knows:
         bq = _c_int(0)
         if L.bg_attention_tc_plan(group, hd, page_size, ctypes.byref(bq)) == 0:
             return "tc_rows", bq.value, 64
@@ -573,7 +579,7 @@ def _attention(q: torch.Tensor, q_stride: int, kv_pool: torch.Tensor, block_tabl
         sink = True
         if sink_weight.dtype != torch.float32 or sink_weight.numel() != nh or not sink_weight.is_contiguous():
             raise KernelError("attention: the sink's scores are contiguous float32, one per query head")
-    if softcap and kernel != "generic" and "softcap" not in TC_OPTIONS:
+    if softcap and kernel != "generic" and "softcap" not in (TC_OPTIONS if kernel == "tc_rows" else MMA_OPTIONS):
         raise KernelError(f"attention: the kernel '{kernel}' does not squash scores")
     learned = sink_weight is not None
     _i32(positions, "positions"); _i32(block_table, "block_table")
@@ -615,7 +621,7 @@ def _attention(q: torch.Tensor, q_stride: int, kv_pool: torch.Tensor, block_tabl
             raise KernelError("attention: the tensor-core kernel takes bfloat16 queries, caches and outputs")
         _check(L.bg_attention_mma_partial(_p(q), q_stride, _p(kv_pool), num_pages, page_size, _p(block_table),
                                           block_table.shape[1], _p(positions), _p(qblk), n_qblk, None, None, 1, 1,
-                                          nh, nkv, hd, window, split, 0, float(scale), _p(out), out.stride(0),
+                                          nh, nkv, hd, window, split, 0, float(scale), float(softcap), _p(out), out.stride(0),
                                           _p(status), _stream()), "attention_mma")
         return
     if kernel == "mma_keys":
@@ -625,7 +631,7 @@ def _attention(q: torch.Tensor, q_stride: int, kv_pool: torch.Tensor, block_tabl
                 raise KernelError("attention: the tensor-core kernel takes bfloat16 queries, caches and outputs")
             _check(L.bg_attention_mma_partial(_p(q), q_stride, _p(kv_pool), num_pages, page_size, _p(block_table),
                                               block_table.shape[1], _p(positions), _p(qblk) if qblk is not None else None,
-                                              n_qblk, None, None, 1, 1, nh, nkv, hd, window, 0, 1, float(scale), _p(out),
+                                              n_qblk, None, None, 1, 1, nh, nkv, hd, window, 0, 1, float(scale), float(softcap), _p(out),
                                               out.stride(0), _p(status), _stream()), "attention_mma_keys")
             return
     else:
@@ -647,7 +653,7 @@ def _attention(q: torch.Tensor, q_stride: int, kv_pool: torch.Tensor, block_tabl
                                           n_qblk, _p(part_o),
                                           _p(part_ml), n_splits, n_splits, nh, nkv, hd, window, split,
                                           1 if kernel == "mma_keys" else 0,
-                                          float(scale), None, 0, _p(status), _stream()), "attention_mma_partial")
+                                          float(scale), float(softcap), None, 0, _p(status), _stream()), "attention_mma_partial")
     else:
         raise KernelError(f"unknown attention kernel '{kernel}'")
     _check(L.bg_attention_merge(_p(part_o), _p(part_ml), _p(positions), _p(out), _dt(out), out.stride(0), n_rows, nh,
@@ -1328,14 +1334,29 @@ def sigmoid_gate(out: torch.Tensor, gate: torch.Tensor, col0: int, n: int, src: 
                                      gate.stride(-2), parts, stride, col0, T, n, int(gate_per), _stream()), "sigmoid_gate")
 
 
+def decay_attention_chunk(n: int, nv: int) -> int:
+    """The number of tokens in a chunk of the chunked kernels for heads of n x nv values, 0 when they do not take them."""
+    c = _c_int(0)
+    return c.value if lib().bg_decay_attention_chunk_plan(int(n), int(nv), ctypes.byref(c)) == 0 else 0
+
+
 def decay_attention(src: torch.Tensor, q_col: int, k_col: int, v_col: int, decay: torch.Tensor, state: torch.Tensor,
-                    slots: torch.Tensor, reqs: torch.Tensor, n_req: int, y: torch.Tensor, H: int, n: int, nv: int) -> None:
+                    slots: torch.Tensor, reqs: torch.Tensor, n_req: int, y: torch.Tensor, H: int, n: int, nv: int,
+                    chunks: Optional[torch.Tensor] = None, n_chunks: int = 0, longs: Optional[torch.Tensor] = None,
+                    n_long: int = 0) -> None:
     """Linear attention with a constant decay per head.  `src` [T, W] (or float partial sums [parts, T, W]) holds, from the
     columns given, the products for q, k ([H, n] each) and v ([H, nv]); q, k, v = silu of them.  Per request (`reqs`
     [n_req, 3] = request, first row, rows) and head, for its rows in turn: S <- decay[h] S + k v^T, y = S^T q, with S
-    [n, nv] float32 at state[slots[request], h * n * nv ...], read at the start and written back at the end."""
-    _cuda(src, decay, state, slots, reqs, y)
-    _i32(slots, "slots"); _i32(reqs, "reqs")
+    [n, nv] float32 at state[slots[request], h * n * nv ...], read at the start and written back at the end.
+
+    Requests of many rows may be given apart, cut into chunks of `decay_attention_chunk(n, nv)` rows: `chunks`
+    [n_chunks, 4] = (request, first row, rows, -) and `longs` [n_long, 4] = (request, first row, rows, index of the first
+    chunk).  Their chunks run in parallel (sums of a chunk's own k v^T, a pass over the chunks' states, the outputs); the
+    results are those of the walk token by token up to rounding.  A request stands in `reqs` or in `longs`, not both."""
+    _cuda(src, decay, state, slots, reqs, y, chunks, longs)
+    _i32(slots, "slots")
+    if n_req:
+        _i32(reqs, "reqs")
     parts, stride = _parts(src, "decay_attention: src")
     T, W = src.shape[-2:]
     if src.stride(-1) != 1 or max(q_col + H * n, k_col + H * n, v_col + H * nv) > W:
@@ -1347,8 +1368,18 @@ def decay_attention(src: torch.Tensor, q_col: int, k_col: int, v_col: int, decay
     if y.dtype != torch.float32 or tuple(y.shape) != (T, H * nv) or not y.is_contiguous():
         raise KernelError(f"decay_attention: y is float32 {(T, H * nv)}")
     with phase("scan"):
-        _check(lib().bg_decay_attention(_p(src), _dt(src), src.stride(-2), parts, stride, q_col, k_col, v_col, _p(decay), _p(state),
-                                        state.stride(0), _p(slots), _p(reqs), n_req, _p(y), H, n, nv, _stream()), "decay_attention")
+        if n_req:
+            _check(lib().bg_decay_attention(_p(src), _dt(src), src.stride(-2), parts, stride, q_col, k_col, v_col, _p(decay),
+                                            _p(state), state.stride(0), _p(slots), _p(reqs), n_req, _p(y), H, n, nv, _stream()),
+                   "decay_attention")
+        if n_chunks:
+            _i32(chunks, "chunks"); _i32(longs, "longs")
+            if chunks.shape[0] < n_chunks or longs.shape[0] < n_long or n_long < 1:
+                raise KernelError("decay_attention: the lists of chunks and of long requests are shorter than their counts")
+            work = torch.empty((n_chunks, H, n * nv), dtype=torch.float32, device=y.device)
+            _check(lib().bg_decay_attention_chunked(_p(src), _dt(src), src.stride(-2), parts, stride, q_col, k_col, v_col, _p(decay),
+                                                    _p(state), state.stride(0), _p(slots), _p(chunks), n_chunks, _p(longs), n_long,
+                                                    _p(work), _p(y), H, n, nv, _stream()), "decay_attention_chunked")
 
 
 def add_terms_norm(x: torch.Tensor, terms, assign: bool = False, weight1: Optional[torch.Tensor] = None,

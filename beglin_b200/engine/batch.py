@@ -29,6 +29,23 @@ class Entry:
         return a
 
 
+def cut_long_requests(row_start: Sequence[int], lens: Sequence[int], bq: int, min_rows: int):
+    """Requests of fewer than `min_rows` rows whole, the others cut into blocks of `bq` rows: int32 arrays
+    short [n, 3] = (request, first row, rows), blocks [n, 4] = (request, first row, rows <= bq, 0) in request order and
+    longs [n, 4] = (request, first row, rows, index of the request's first block)."""
+    short, blocks, longs = [], [], []
+    for i, (r0, n) in enumerate(zip(row_start, lens)):
+        if n <= 0:
+            continue
+        if n < min_rows:
+            short.append((i, r0, n))
+            continue
+        longs.append((i, r0, n, len(blocks)))
+        blocks += [(i, r0 + f, min(bq, n - f), 0) for f in range(0, n, bq)]
+    arr = lambda rows, w: np.asarray(rows, dtype=np.int32).reshape(-1, w)
+    return arr(short, 3), arr(blocks, 4), arr(longs, 4)
+
+
 ALIGN = 32      # every array of a step starts on a multiple of this many int32 values (128 bytes) of the one buffer
 
 
@@ -75,6 +92,17 @@ class StepBatch:
         self.slots: Optional[torch.Tensor] = dev.get("slots")
         self.scratch: Dict[object, object] = {}       # per-step tables made by parts (rotary tables)
         self._qblk: Dict[int, Tuple[torch.Tensor, int]] = {}
+
+    def long_blocks(self, bq: int, min_rows: int):
+        """`cut_long_requests` of this step on the device: (short, n, blocks, n, longs, n), one upload."""
+        key = ("long", bq, min_rows)
+        hit = self._qblk.get(key)
+        if hit is None:
+            short, blocks, longs = cut_long_requests(self.row_start, self.lens, bq, min_rows)
+            dev = self._to_device_packed({"short": short, "blocks": blocks, "longs": longs})
+            hit = self._qblk[key] = (dev["short"], int(short.shape[0]), dev["blocks"], int(blocks.shape[0]),
+                                     dev["longs"], int(longs.shape[0]))
+        return hit
 
     def _to_device_packed(self, arrays: Dict[object, np.ndarray]) -> Dict[object, torch.Tensor]:
         """int32 arrays -> device tensors of the same shapes, through one buffer and one copy."""

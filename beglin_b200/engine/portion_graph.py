@@ -22,7 +22,7 @@ import numpy as np
 import torch
 
 from ..csrc import ops
-from .batch import ALIGN
+from .batch import ALIGN, cut_long_requests
 from .capture import no_collection
 
 
@@ -69,6 +69,17 @@ class _StaticPortion:
             arr = np.stack([np.zeros(first.size, dtype=np.int32), first,
                             np.minimum(bq, self.n_rows - first).astype(np.int32)], axis=1)
             hit = self._qblk[bq] = (torch.from_numpy(arr).to(self.device), int(arr.shape[0]))
+        return hit
+
+
+    def long_blocks(self, bq: int, min_rows: int):
+        key = ("long", bq, min_rows)
+        hit = self._qblk.get(key)
+        if hit is None:
+            arrays = cut_long_requests([0], [self.n_rows], bq, min_rows)
+            dev = [torch.from_numpy(a).to(self.device) for a in arrays]
+            hit = self._qblk[key] = (dev[0], int(arrays[0].shape[0]), dev[1], int(arrays[1].shape[0]), dev[2],
+                                     int(arrays[2].shape[0]))
         return hit
 
 

@@ -9,6 +9,11 @@ weight, multiplied feature by feature by sigmoid(g), and go through the output p
 The state S is per-request state of fixed size (one slot of the cache manager's slab, float32, zero when the request
 starts): a step continues each request from its slot, however the request's tokens are cut into steps and whatever else
 the step holds.  State, decay, the products that enter the state and the readout are float in both number formats.
+
+A request that brings many rows runs in chunks of tokens: with S the state at a chunk's start and t, j counting the
+chunk's r tokens from 0, o_t = d^(t+1) S^T q_t + sum_{j <= t} d^(t-j) (q_t . k_j) v_j and the state behind the chunk is
+d^r S + sum_j d^(r-1-j) k_j v_j^T, so the chunks' own sums and outputs are computed side by side and only a pass over
+the chunks' states is serial.
 """
 from __future__ import annotations
 
@@ -54,6 +59,9 @@ class DecayAttention:
         self.norm_w = ctx.vector(tensors["norm.weight"])
         self.decay = torch.tensor([float(d) for d in spec.decay], dtype=torch.float32, device=ctx.device)
         self.g_col = 2 * self.qd + self.vd
+        self.chunk = ops.decay_attention_chunk(spec.dim, spec.vdim) if ctx.device.type == "cuda" else 0
+
+    LONG_FROM = 16             # rows of a request in a step from which its tokens run in chunks
 
     takes_stream = True        # forward takes a NormedInput and may add its result to the stream itself
 
@@ -65,10 +73,15 @@ class DecayAttention:
         s = self.spec
         T = batch.n_rows
         proj = self.in_proj(h, out_dtype=torch.float32)                 # [T, q | k | v | g]
-        reqs, n_req = batch.query_blocks(1 << 30)                       # one (request, first row, rows) per request
         y = torch.empty((T, self.vd), dtype=torch.float32, device=h.device)
+        if self.chunk and not batch.decode_only and hasattr(batch, "long_blocks"):
+            # requests of LONG_FROM rows and more in chunks, the others token by token
+            reqs, n_req, chunks, n_chunks, longs, n_long = batch.long_blocks(self.chunk, self.LONG_FROM)
+        else:
+            reqs, n_req = batch.query_blocks(1 << 30)                   # one (request, first row, rows) per request
+            chunks, n_chunks, longs, n_long = None, 0, None, 0
         ops.decay_attention(proj, 0, self.qd, 2 * self.qd, self.decay, cache.state, cache.slots, reqs, n_req, y,
-                            s.n_heads, s.dim, s.vdim)
+                            s.n_heads, s.dim, s.vdim, chunks, n_chunks, longs, n_long)
         out = torch.empty((T, self.vd), dtype=self.ctx.compute_dtype, device=h.device)
         ops.gated_group_rmsnorm(y, proj, self.g_col, self.norm_w, s.eps, 1, out, gate_after=True)
         if stream is None:
