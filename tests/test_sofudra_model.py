@@ -62,7 +62,7 @@ def test_four_ways_of_cutting(model_root, name, dtype):
     if dtype == "float32":
         for way in ("tail", "portions", "mixed"):
             for key, row in results["whole"].items():
-                assert rel_err(results[way][key], row) < TOL_F32, (way, key)
+                assert rel_err(results[way][key], row) < 2 * TOL_F32, (way, key)
 
 
 @pytest.mark.parametrize("name", ["odd", "even", "sharp"])

@@ -1,7 +1,8 @@
 """Random configurations of the Sofudra decoder: `random_config(case)` is a pure function of the case number and draws
 every size, the kinds and the order of the layers, which of them a loop takes in and how often, the windows and the
 constants; each case runs whole and mixed with other requests on a small pool, in float32 and in bfloat16, against the
-oracle.  The bfloat16 cases draw sizes in multiples of 8 (what the tensor-core products take)."""
+oracle.  The bfloat16 cases draw sizes in multiples of 8 (what the tensor-core products take).  The decayed states have
+at least four values per head: the norm behind a single value keeps its sign only, which rounding flips near nought."""
 import random
 
 import pytest
@@ -39,7 +40,7 @@ def random_config(case: int, even: bool = False):
         else:
             dh = rng.randrange(1, 5)
             dn = rng.choice([16, 32, 64]) if even else rng.randrange(1, 40)
-            dv = rng.choice([16, 32, 64]) if even else rng.randrange(1, 40)
+            dv = rng.choice([16, 32, 64]) if even else rng.randrange(4, 40)
             decay = [rng.choice([0.0, 1.0, rng.uniform(0.3, 0.999), rng.uniform(0.9, 0.9999)]) for _ in range(dh)]
             mixer = par(gated(heads, kv, dim, vdim, scale, rng.choice([1.0, 5.0, 30.0, 100.0])), decayed(dh, dn, dv, decay),
                         rng.uniform(0.5, 1.5), rng.uniform(0.5, 1.5))
@@ -72,4 +73,4 @@ def test_random_configuration(model_root, case, dtype):
         check_against_plain(results[way], folder, reqs, TOL_F32 if dtype == "float32" else TOL_BF16)
     if dtype == "float32":
         for key, row in results["whole"].items():
-            assert rel_err(results["mixed"][key], row) < TOL_F32, key
+            assert rel_err(results["mixed"][key], row) < 2 * TOL_F32, key      # (two roundings of their own)
