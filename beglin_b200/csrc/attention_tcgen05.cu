@@ -58,6 +58,9 @@ struct AttnTcParams {
     int out_stride;
     int nh, nkv, group, window;
     float scale_log2;
+    float cap_log2;             // c * log2(e) when scores are squashed to c tanh(score / c), else 0
+    float cap_k;                // 2 * log2(e) * scale / c
+    const float* sink_weight;   // [nh] the sink's score head by head (null: 0), where the denominator is enlarged
     unsigned* status;
 };
 
@@ -70,6 +73,14 @@ __device__ __forceinline__ float at_ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
     return y;
+}
+
+// c log2(e) tanh(scale * x / c) as 1 - 2 / (1 + 2^(2 log2(e) scale x / c)): two special-function operations, exact at both
+// ends (2^inf = inf gives 1, 2^-inf = 0 gives -1), and a few units in the last place elsewhere.
+__device__ __forceinline__ float at_squash(float x, float cap_log2, float cap_k) {
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;\n" : "=f"(r) : "f"(1.0f + at_ex2(x * cap_k)));
+    return cap_log2 * fmaf(-2.0f, r, 1.0f);
 }
 
 // SINK: the softmax's denominator is enlarged by one (a key of score 0 without a value): the final join takes 0 into the
@@ -258,6 +269,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
         const int warp_lo_max = __reduce_max_sync(0xffffffffu, lo);
         float m = -INFINITY, l = 0.0f;
         bool ok = true;
+        const bool capped = p.cap_log2 > 0.0f;
+        const float sl2 = capped ? 1.0f : p.scale_log2;
         const int i_first = ALT ? grp : 0;                   // this group's first tile
         for (int i = i_first; i < n_tiles && ok; i += (ALT ? 2 : 1)) {
             const int b = i % NSB;
@@ -269,6 +282,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
             float s[GK];
             if constexpr (GK == 64) tc_ld64(tmem + lane_addr + s_col, s);
             else tc_ld32(tmem + lane_addr + s_col, s);
+            if (capped) {                                // squashed scores come out as exponents of two
+#pragma unroll
+                for (int q = 0; q < GK; ++q) s[q] = at_squash(s[q], p.cap_log2, p.cap_k);
+            }
             // only a half that some row of the warp sees in part is masked element by element
             float tm[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
             if (key0 + GK - 1 > warp_pos_min || key0 < warp_lo_max) {
@@ -282,7 +299,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
 #pragma unroll
                 for (int q = 0; q < GK; ++q) tm[q & 3] = fmaxf(tm[q & 3], s[q]);
             }
-            const float tmax = fmaxf(fmaxf(tm[0], tm[1]), fmaxf(tm[2], tm[3])) * p.scale_log2;   // the scale is positive
+            const float tmax = fmaxf(fmaxf(tm[0], tm[1]), fmaxf(tm[2], tm[3])) * sl2;   // the scale is positive
             // The reference maximum m moves only when some row of the warp outgrows it by more than 8 (a factor
             // of 256, harmless in float and bfloat16): then the rows' O and l are rescaled; otherwise the
             // exponentials keep the old reference and nothing that was accumulated needs touching.
@@ -294,7 +311,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
             float pk[GK / 2];                            // P: two keys a column
 #pragma unroll
             for (int c = 0; c < GK / 2; ++c) {
-                const float e0 = at_ex2(fmaf(s[2 * c], p.scale_log2, -m_use)), e1 = at_ex2(fmaf(s[2 * c + 1], p.scale_log2, -m_use));
+                const float e0 = at_ex2(fmaf(s[2 * c], sl2, -m_use)), e1 = at_ex2(fmaf(s[2 * c + 1], sl2, -m_use));
                 sums[c & 3] += e0 + e1;
                 const __nv_bfloat162 h2 = __floats2bfloat162_rn(e0, e1);
                 pk[c] = __uint_as_float(*reinterpret_cast<const unsigned*>(&h2));
@@ -334,13 +351,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
             tc_fence_after();
             const float2 other = ml_other[r];
             const float m_all = fmaxf(m, other.x);
-            const float m_ref = SINK ? fmaxf(m_all, 0.0f) : ((m_all == -INFINITY) ? 0.0f : m_all);
+            const int qi = real ? r / group : 0, g = real ? r - qi * group : 0;
+            const float sink_l2 = (SINK && p.sink_weight) ? p.sink_weight[kvh * group + g] * AT_LOG2E : 0.0f;
+            const float m_ref = SINK ? fmaxf(m_all, sink_l2) : ((m_all == -INFINITY) ? 0.0f : m_all);
             const float a0 = at_ex2(m - m_ref), a1 = at_ex2(other.x - m_ref);
-            const float l_all = l * a0 + other.y * a1 + (SINK ? at_ex2(-m_ref) : 0.0f);
+            const float l_all = l * a0 + other.y * a1 + (SINK ? at_ex2(sink_l2 - m_ref) : 0.0f);
             const float inv = (real && l_all > 0.0f) ? 1.0f / l_all : 0.0f;
             const float w0 = a0 * inv, w1 = a1 * inv;
             const bool has1 = !ALT || n_tiles > 1;       // with one tile the second group's accumulator was never written
-            const int qi = real ? r / group : 0, g = real ? r - qi * group : 0;
             __nv_bfloat16* o = p.out + (size_t)(row0 + qi) * p.out_stride + (size_t)(kvh * group + g) * HD;
 #pragma unroll
             for (int c0 = 0; c0 < HD; c0 += 32) {
@@ -493,8 +511,9 @@ extern "C" int bg_attention_tc_plan(int group, int hd, int page_size, int* bq_ou
 static int attention_tc(const void* q, int q_stride, const void* kv_pool, int num_pages, int page_size,
                         const int* block_table, int max_pages, const int* positions, const int* qblk, int n_qblk,
                         void* out, int out_stride, int nh, int nkv, int hd, int window, float scale, int max_position,
-                        bool sink, unsigned* status, cudaStream_t stream) {
+                        bool sink, unsigned* status, cudaStream_t stream, const float* sink_weight = nullptr, float softcap = 0.0f) {
     if (n_qblk <= 0) return BG_OK;
+    if ((sink_weight && !sink) || softcap < 0.0f) return BG_ERR_SHAPE;
     if (nh % nkv != 0 || (hd != 64 && hd != 128) || nh / nkv > 128 || !(scale > 0.0f)) return BG_ERR_UNSUPPORTED;
     if (page_size < 1 || page_size > 64 || 64 % page_size != 0) return BG_ERR_UNSUPPORTED;
     if ((q_stride % 8) || (out_stride % 8) || ((uintptr_t)q % 16) || ((uintptr_t)kv_pool % 16) || ((uintptr_t)out % 16)) return BG_ERR_ALIGN;
@@ -506,6 +525,8 @@ static int attention_tc(const void* q, int q_stride, const void* kv_pool, int nu
     p.block_table = block_table; p.max_pages = max_pages; p.positions = positions; p.qblk = qblk;
     p.out = (__nv_bfloat16*)out; p.out_stride = out_stride; p.nh = nh; p.nkv = nkv; p.group = nh / nkv;
     p.window = window; p.scale_log2 = scale * AT_LOG2E; p.status = status;
+    p.cap_log2 = softcap > 0.0f ? softcap * AT_LOG2E : 0.0f; p.cap_k = softcap > 0.0f ? 2.0f * AT_LOG2E * scale / softcap : 0.0f;
+    p.sink_weight = sink_weight;
     CUtensorMap map;
     int rc = pt_pool_map(&map, kv_pool, num_pages, nkv, page_size, hd);
     if (rc != BG_OK) return rc;
@@ -534,4 +555,15 @@ extern "C" int bg_attention_tc_sink(const void* q, int q_stride, const void* kv_
                                     unsigned* status, cudaStream_t stream) {
     return attention_tc(q, q_stride, kv_pool, num_pages, page_size, block_table, max_pages, positions, qblk, n_qblk, out, out_stride,
                         nh, nkv, hd, window, scale, max_position, true, status, stream);
+}
+
+// The same with what a layer may add to the softmax: a sink's score for every query head (float [nh]; null with `sink`
+// set: a score of 0; `sink` 0: none) and scores squashed to softcap * tanh(score / softcap) (0: as they are).
+extern "C" int bg_attention_tc_ext(const void* q, int q_stride, const void* kv_pool, int num_pages, int page_size,
+                                   const int* block_table, int max_pages, const int* positions, const int* qblk, int n_qblk,
+                                   void* out, int out_stride, int nh, int nkv, int hd, int window, float scale, int max_position,
+                                   int sink, const float* sink_weight, float softcap, unsigned* status, cudaStream_t stream) {
+    return attention_tc(q, q_stride, kv_pool, num_pages, page_size, block_table, max_pages, positions, qblk, n_qblk, out, out_stride,
+                        nh, nkv, hd, window, scale, max_position, sink != 0 || sink_weight != nullptr, status, stream, sink_weight,
+                        softcap);
 }

@@ -75,6 +75,9 @@ _SIGNATURES = {
     "bg_attention_tc_plan": [_c_int, _c_int, _c_int, ctypes.POINTER(_c_int)],
     "bg_attention_tc": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int,
                         _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void_p, _c_void_p],
+    "bg_attention_tc_ext": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int,
+                            _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_void_p, _c_float,
+                            _c_void_p, _c_void_p],
     "bg_attention_tc_sink": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int,
                              _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void_p, _c_void_p],
     "bg_gemm_f32_nt": [_c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
@@ -478,7 +481,7 @@ def attention_wide_from(keys: int = 0) -> int:
 
 
 TC_ROWS_FOR = ("auto", "tcgen05")
-TC_OPTIONS = ()                                # options of the softmax that the tcgen05 kernel knows besides the plain one
+TC_OPTIONS = ("softcap", "sink_weight")        # options of the softmax that the tcgen05 kernel knows besides the plain one
 MMA_OPTIONS = ("softcap", "sink_weight")       # ... and the mma kernels (the sink's share is added where partial results merge)
 SINK_KERNELS = ("generic", "tc_rows", "mma_keys", "mma_rows")   # every kernel can take the enlarged denominator (`sink`)
 
@@ -611,6 +614,12 @@ def _attention(q: torch.Tensor, q_stride: int, kv_pool: torch.Tensor, block_tabl
     if kernel == "tc_rows":
         if q.dtype != torch.bfloat16 or kv_pool.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
             raise KernelError("attention: the tcgen05 kernel takes bfloat16 queries, caches and outputs")
+        if learned or softcap:
+            _check(L.bg_attention_tc_ext(
+                _p(q), q_stride, _p(kv_pool), num_pages, page_size, _p(block_table), block_table.shape[1], _p(positions),
+                _p(qblk), n_qblk, _p(out), out.stride(0), nh, nkv, hd, window, float(scale), int(max_position),
+                1 if sink else 0, _p(sink_weight), float(softcap), _p(status), _stream()), "attention_tcgen05")
+            return
         _check((L.bg_attention_tc_sink if sink else L.bg_attention_tc)(
             _p(q), q_stride, _p(kv_pool), num_pages, page_size, _p(block_table), block_table.shape[1], _p(positions), _p(qblk),
             n_qblk, _p(out), out.stride(0), nh, nkv, hd, window, float(scale), int(max_position), _p(status), _stream()),

@@ -385,9 +385,33 @@ def nadilorn_config(width, heads, layers, vocab=32768, vdim=128):
             "layers": [{"type": "attention", "mixer": mixer, "mlp": dense if i == 0 else moe} for i in range(layers)]}
 
 
+# The Sofudra decoder beside another design at equal layer sizes (--design sofudra): a first layer of grouped-query
+# attention with heads of 128 features normed one by one, whole heads rotated with stretched frequencies, a window of
+# 1,024 positions and a learned sink; then layers of two mixers side by side (attention without rotation, scores squashed
+# at 30, one gate per head; beside it linear attention with a constant decay per head, width / 128 heads of 128 x 128
+# values of state), every layer with a dense GELU feed-forward of the Qwen2 layer's weights (two matrices of 3/2 its inner
+# size) read from the same stream as the mixer.  Two of the layers are passed twice with the input mix in front, so that
+# the number of layer runs is the other model's number of layers.  Random weights.
+def sofudra_config(width, heads, layers, vocab=32768):
+    kv = max(1, heads // 4 if heads % 4 == 0 and heads > 12 else heads // 6)
+    first = {"heads": heads, "kv_heads": kv, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": 1024},
+             "rot": {"base": 500000.0, "dims": 128, "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}}}
+    left = {"heads": heads, "kv_heads": kv, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 30.0}
+    dh = width // 128
+    right = {"heads": dh, "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** (-3.0 - 5.0 * i / max(1, dh - 1)) for i in range(dh)]}
+    ff = {"kind": "dense", "ff": (4 * width) // 128 * 128}
+    par = {"left": left, "right": right, "left_scale": 1.0, "right_scale": 1.0}
+    k = 2 if layers >= 5 else 1                    # layers passed twice
+    n = layers - k
+    return {"architecture": "Sofudra", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "embedding": {"scale": float(width) ** 0.5},
+            "residual_mult": 0.5, "logit_softcap": 30.0, "loop": {"start": 1, "stop": 1 + k, "times": 2},
+            "layers": [{"type": "attention" if i == 0 else "parallel", "mixer": first if i == 0 else par, "mlp": ff} for i in range(n)]}
+
+
 DESIGN_SIZES = {"1536": (1536, 12, 8), "4096": (4096, 32, 4)}      # width -> (width, heads, layers)
 DESIGNS = {"sukisun": lambda w, h, l: sukisun_config(w, h, l), "nadilorn": lambda w, h, l: nadilorn_config(w, h, l),
-           "nadilorn-v64": lambda w, h, l: nadilorn_config(w, h, l, vdim=64)}
+           "nadilorn-v64": lambda w, h, l: nadilorn_config(w, h, l, vdim=64), "sofudra": lambda w, h, l: sofudra_config(w, h, l)}
+BESIDE = dict(DESIGNS, qwen2=lambda w, h, l: qwen2_like(w, h, l))
 
 
 def phase_times(eng, fn):
@@ -412,7 +436,10 @@ def design_point(cfg, pk, batch, context, steps, warmup, tokens):
     page = 64
     eng = Engine.random(cfg, seed=0, dtype="bfloat16", device="cuda:0", max_tokens=batch * (context + page), page_size=page,
                         max_requests=batch, max_context=context + page)
-    out = {"weight_gb": round(eng.model.weight_bytes() / 1e9, 3), "cache_bytes_per_token": eng.cache.device_bytes() // max(1, eng.cache.num_pages + 1) // page}
+    kv_bytes = sum(g.device_pool.numel() * g.device_pool.element_size() for g in eng.cache.kv_groups if g.device_pool is not None)
+    state_bytes = eng.cache.device_bytes() - kv_bytes      # per-request state of fixed size: read and written every step
+    out = {"weight_gb": round(eng.model.weight_bytes() / 1e9, 3), "cache_bytes_per_token": kv_bytes // max(1, eng.cache.num_pages + 1) // page,
+           "state_bytes_per_request": state_bytes // max(1, batch)}
     pms = time_prefill(eng, tokens, reps=3, seed=3)
     out["prefill_tok_s"] = round(tokens * 1000.0 / pms, 1)
     out["prefill_ms"] = round(pms, 3)
@@ -426,7 +453,7 @@ def design_point(cfg, pk, batch, context, steps, warmup, tokens):
     # (a layer with a window reads no more of a request's positions than the window holds)
     windows = [l["mixer"].get("mask", {}).get("size") for l in cfg.get("layers", []) if isinstance(l.get("mixer"), dict)]
     seen = min([context - steps / 2.0] + [w for w in windows if w]) if windows and all(windows) else context - steps / 2.0
-    step_bytes = eng.model.weight_bytes() + batch * seen * out["cache_bytes_per_token"]
+    step_bytes = eng.model.weight_bytes() + batch * seen * out["cache_bytes_per_token"] + 2 * state_bytes
     out["decode_frac_of_hbm"] = round(step_bytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
     rids = [("cls", i) for i in range(batch)]
     fill_cache(eng, rids, context - 8, seed=4)
@@ -460,9 +487,10 @@ def design_comparison(args, pk):
     rows = {}
     for name in args.design_sizes.split(","):
         width, heads, layers = DESIGN_SIZES[name]
-        for label, cfg in ((args.design, DESIGNS[args.design](width, heads, layers)), ("qwen2", qwen2_like(width, heads, layers))):
+        for label, cfg in [(args.design, DESIGNS[args.design](width, heads, layers))] + \
+                          [(b, BESIDE[b](width, heads, layers)) for b in args.beside.split(",") if b]:
             rows[f"{label}_{name}"] = design_point(cfg, pk, args.batch, args.context, min(args.steps, 32), args.warmup, 2048)
-    print(json.dumps({"design": f"{args.design} beside qwen2 at equal layer sizes", "dtype": "bf16", "batch": args.batch,
+    print(json.dumps({"design": f"{args.design} beside {args.beside} at equal layer sizes", "dtype": "bf16", "batch": args.batch,
                       "context": args.context, "data": "synthetic (seeded uniform token ids, random weights)",
                       "peaks": pk, "clocks": clocks.stop(), "points": rows}))
     return 0
@@ -488,6 +516,7 @@ def main():
     ap.add_argument("--design", default=None, choices=sorted(DESIGNS),
                     help="instead of the headline measurement: this design beside Qwen2 at equal layer sizes, prefill and "
                          "decode, with the device time per kernel class")
+    ap.add_argument("--beside", default="qwen2", help="what --design is measured beside: a list of " + ",".join(sorted(BESIDE)))
     ap.add_argument("--design-sizes", default="1536,4096", help="widths to compare at, of " + ",".join(sorted(DESIGN_SIZES)))
     args = ap.parse_args()
 

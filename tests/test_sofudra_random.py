@@ -2,7 +2,9 @@
 every size, the kinds and the order of the layers, which of them a loop takes in and how often, the windows and the
 constants; each case runs whole and mixed with other requests on a small pool, in float32 and in bfloat16, against the
 oracle.  The bfloat16 cases draw sizes in multiples of 8 (what the tensor-core products take).  The decayed states have
-at least four values per head: the norm behind a single value keeps its sign only, which rounding flips near nought."""
+at least four values per head and decays of 0.3 and more: the norm behind a single value keeps its sign only, and with
+a decay of nought a head's output is its value times q . k, of which the norm again keeps the sign, which rounding flips
+near nought (a decay of nought runs in the tests of the kernels, in front of the norm)."""
 import random
 
 import pytest
@@ -41,7 +43,7 @@ def random_config(case: int, even: bool = False):
             dh = rng.randrange(1, 5)
             dn = rng.choice([16, 32, 64]) if even else rng.randrange(1, 40)
             dv = rng.choice([16, 32, 64]) if even else rng.randrange(4, 40)
-            decay = [rng.choice([0.0, 1.0, rng.uniform(0.3, 0.999), rng.uniform(0.9, 0.9999)]) for _ in range(dh)]
+            decay = [rng.choice([0.3, 1.0, rng.uniform(0.3, 0.999), rng.uniform(0.9, 0.9999)]) for _ in range(dh)]
             mixer = par(gated(heads, kv, dim, vdim, scale, rng.choice([1.0, 5.0, 30.0, 100.0])), decayed(dh, dn, dv, decay),
                         rng.uniform(0.5, 1.5), rng.uniform(0.5, 1.5))
         layers.append(layer(mixer, rng.choice([None, unit * rng.randrange(2, 30), unit * rng.randrange(2, 30)])))
