@@ -123,8 +123,24 @@ __device__ __forceinline__ void decay_powers(float* pw, float d) {      // pw[k]
         acc[3][0] = fmaf(a.w, b.x, acc[3][0]); acc[3][1] = fmaf(a.w, b.y, acc[3][1]); acc[3][2] = fmaf(a.w, b.z, acc[3][2]); acc[3][3] = fmaf(a.w, b.w, acc[3][3]); \
     } while (0)
 
+
+// Fills of shared memory from the rows of a chunk go eight loads at a time per thread: the loads of a batch are in
+// flight together, and the activations follow when they have landed.
+constexpr int DA_BATCH = 8;
+constexpr int DC_THREADS = 512;
+
+// The (row, column) of element tid + k * blockDim.x of a [rows][w] tile, stepped without a division per element.
+struct TileWalk {
+    int j, i, dj, di, w;
+    __device__ __forceinline__ TileWalk(int w_) : w(w_) {
+        j = (int)threadIdx.x / w; i = (int)threadIdx.x - j * w;
+        dj = (int)blockDim.x / w; di = (int)blockDim.x - dj * w;
+    }
+    __device__ __forceinline__ void next() { i += di; j += dj; if (i >= w) { i -= w; ++j; } }
+};
+
 template <typename TS>
-__global__ void __launch_bounds__(256) decay_chunk_sum_kernel(DecayChunkParams p) {
+__global__ void __launch_bounds__(DC_THREADS) decay_chunk_sum_kernel(DecayChunkParams p) {
     extern __shared__ __align__(16) float dc_s[];
     const int n = p.n, nv = p.nv, np = p.np, nvp = p.nvp;
     float* Ks = dc_s;                          // [DC][np], k_j times d^(r-1-j)
@@ -137,19 +153,29 @@ __global__ void __launch_bounds__(256) decay_chunk_sum_kernel(DecayChunkParams p
     const int row0 = p.chunks[c * 4 + 1], rows = p.chunks[c * 4 + 2];
     __syncthreads();
     const TS* src = (const TS*)p.src;
-    for (int idx = tid; idx < DC * np; idx += blockDim.x) {
-        const int j = idx / np, i = idx - j * np;
-        float v = 0.0f;
-        if (j < rows && i < n)
-            v = da_silu(sum_parts(src + (size_t)(row0 + j) * p.src_stride + p.k_col + h * n + i, p.parts, p.part_stride)) * pw[rows - 1 - j];
-        Ks[idx] = v;
+    for (TileWalk w(np); w.j < DC;) {
+        float raw[DA_BATCH];
+        int jj[DA_BATCH], ii[DA_BATCH];
+#pragma unroll
+        for (int u = 0; u < DA_BATCH; ++u) {
+            jj[u] = w.j; ii[u] = w.i; w.next();
+            raw[u] = (jj[u] < rows && ii[u] < n) ? sum_parts(src + (size_t)(row0 + jj[u]) * p.src_stride + p.k_col + h * n + ii[u], p.parts, p.part_stride) : -INFINITY;
+        }
+#pragma unroll
+        for (int u = 0; u < DA_BATCH; ++u)
+            if (jj[u] < DC) Ks[jj[u] * np + ii[u]] = raw[u] == -INFINITY ? 0.0f : da_silu(raw[u]) * pw[rows - 1 - jj[u]];
     }
-    for (int idx = tid; idx < DC * nvp; idx += blockDim.x) {
-        const int j = idx / nvp, i = idx - j * nvp;
-        float v = 0.0f;
-        if (j < rows && i < nv)
-            v = da_silu(sum_parts(src + (size_t)(row0 + j) * p.src_stride + p.v_col + h * nv + i, p.parts, p.part_stride));
-        Vs[idx] = v;
+    for (TileWalk w(nvp); w.j < DC;) {
+        float raw[DA_BATCH];
+        int jj[DA_BATCH], ii[DA_BATCH];
+#pragma unroll
+        for (int u = 0; u < DA_BATCH; ++u) {
+            jj[u] = w.j; ii[u] = w.i; w.next();
+            raw[u] = (jj[u] < rows && ii[u] < nv) ? sum_parts(src + (size_t)(row0 + jj[u]) * p.src_stride + p.v_col + h * nv + ii[u], p.parts, p.part_stride) : -INFINITY;
+        }
+#pragma unroll
+        for (int u = 0; u < DA_BATCH; ++u)
+            if (jj[u] < DC) Vs[jj[u] * nvp + ii[u]] = raw[u] == -INFINITY ? 0.0f : da_silu(raw[u]);
     }
     __syncthreads();
     float* A = p.work + ((size_t)c * p.H + h) * n * nv;
@@ -177,24 +203,31 @@ __global__ void __launch_bounds__(256) decay_chunk_scan_kernel(DecayChunkParams 
     const int sz = p.n * p.nv;
     if (e >= sz) return;
     const int req = p.longs[l * 4 + 0], rows = p.longs[l * 4 + 2], c0 = p.longs[l * 4 + 3];
+    const int n_chunks = (rows + DC - 1) / DC, last_rows = rows - (n_chunks - 1) * DC;
     const float d = p.decay[h];
-    float dfull = 1.0f;
-    for (int k = 0; k < DC; ++k) dfull *= d;
+    float dfull = 1.0f, dlast = 1.0f;
+    for (int k = 0; k < DC; ++k) { dfull *= d; if (k + 1 == last_rows) dlast = dfull; }
     float* st = p.state + (size_t)p.slots[req] * p.slot_stride + (size_t)h * sz + e;
+    float* a0 = p.work + ((size_t)c0 * p.H + h) * sz + e;
+    const size_t step = (size_t)p.H * sz;
     float S = *st;
-    for (int c = 0, left = rows; left > 0; ++c, left -= DC) {
-        float dr = dfull;
-        if (left < DC) { dr = 1.0f; for (int k = 0; k < left; ++k) dr *= d; }
-        float* a = p.work + ((size_t)(c0 + c) * p.H + h) * sz + e;
-        const float A = *a;
-        *a = S;
-        S = fmaf(dr, S, A);
+    // the chunks' sums are fetched eight at a time, so that the walk waits for memory once per batch and not per chunk
+    for (int c = 0; c < n_chunks; c += DA_BATCH) {
+        float A[DA_BATCH];
+#pragma unroll
+        for (int u = 0; u < DA_BATCH; ++u) A[u] = c + u < n_chunks ? a0[(size_t)(c + u) * step] : 0.0f;
+#pragma unroll
+        for (int u = 0; u < DA_BATCH; ++u)
+            if (c + u < n_chunks) {
+                a0[(size_t)(c + u) * step] = S;
+                S = fmaf(c + u == n_chunks - 1 ? dlast : dfull, S, A[u]);
+            }
     }
     *st = S;
 }
 
 template <typename TS>
-__global__ void __launch_bounds__(256) decay_chunk_out_kernel(DecayChunkParams p) {
+__global__ void __launch_bounds__(DC_THREADS) decay_chunk_out_kernel(DecayChunkParams p) {
     extern __shared__ __align__(16) float dc_s[];
     const int n = p.n, nv = p.nv, np = p.np, nvp = p.nvp;
     float* Qt = dc_s;                          // [np][DCP]
@@ -209,28 +242,50 @@ __global__ void __launch_bounds__(256) decay_chunk_out_kernel(DecayChunkParams p
     pdl_wait();
     const int row0 = p.chunks[c * 4 + 1], rows = p.chunks[c * 4 + 2];
     const TS* src = (const TS*)p.src;
-    for (int idx = tid; idx < DC * np; idx += blockDim.x) {
-        const int j = idx / np, i = idx - j * np;
-        float q = 0.0f, k = 0.0f;
-        if (j < rows && i < n) {
-            const TS* row = src + (size_t)(row0 + j) * p.src_stride + h * n + i;
-            q = da_silu(sum_parts(row + p.q_col, p.parts, p.part_stride));
-            k = da_silu(sum_parts(row + p.k_col, p.parts, p.part_stride));
+    for (TileWalk w(np); w.j < DC;) {
+        float rq[DA_BATCH], rk[DA_BATCH];
+        int jj[DA_BATCH], ii[DA_BATCH];
+#pragma unroll
+        for (int u = 0; u < DA_BATCH; ++u) {
+            jj[u] = w.j; ii[u] = w.i; w.next();
+            rq[u] = rk[u] = -INFINITY;
+            if (jj[u] < rows && ii[u] < n) {
+                const TS* row = src + (size_t)(row0 + jj[u]) * p.src_stride + h * n + ii[u];
+                rq[u] = sum_parts(row + p.q_col, p.parts, p.part_stride);
+                rk[u] = sum_parts(row + p.k_col, p.parts, p.part_stride);
+            }
         }
-        Qt[(size_t)i * DCP + j] = q;
-        Kt[(size_t)i * DCP + j] = k;
+#pragma unroll
+        for (int u = 0; u < DA_BATCH; ++u)
+            if (jj[u] < DC) {
+                Qt[(size_t)ii[u] * DCP + jj[u]] = rq[u] == -INFINITY ? 0.0f : da_silu(rq[u]);
+                Kt[(size_t)ii[u] * DCP + jj[u]] = rk[u] == -INFINITY ? 0.0f : da_silu(rk[u]);
+            }
     }
-    for (int idx = tid; idx < DC * nvp; idx += blockDim.x) {
-        const int j = idx / nvp, i = idx - j * nvp;
-        float v = 0.0f;
-        if (j < rows && i < nv)
-            v = da_silu(sum_parts(src + (size_t)(row0 + j) * p.src_stride + p.v_col + h * nv + i, p.parts, p.part_stride));
-        Vs[idx] = v;
+    for (TileWalk w(nvp); w.j < DC;) {
+        float raw[DA_BATCH];
+        int jj[DA_BATCH], ii[DA_BATCH];
+#pragma unroll
+        for (int u = 0; u < DA_BATCH; ++u) {
+            jj[u] = w.j; ii[u] = w.i; w.next();
+            raw[u] = (jj[u] < rows && ii[u] < nv) ? sum_parts(src + (size_t)(row0 + jj[u]) * p.src_stride + p.v_col + h * nv + ii[u], p.parts, p.part_stride) : -INFINITY;
+        }
+#pragma unroll
+        for (int u = 0; u < DA_BATCH; ++u)
+            if (jj[u] < DC) Vs[jj[u] * nvp + ii[u]] = raw[u] == -INFINITY ? 0.0f : da_silu(raw[u]);
     }
     const float* S0 = p.work + ((size_t)c * p.H + h) * n * nv;
-    for (int idx = tid; idx < np * nvp; idx += blockDim.x) {
-        const int i = idx / nvp, cc = idx - i * nvp;
-        Ss[idx] = (i < n && cc < nv) ? S0[(size_t)i * nv + cc] : 0.0f;
+    for (TileWalk w(nvp); w.j < np;) {
+        float raw[DA_BATCH];
+        int jj[DA_BATCH], ii[DA_BATCH];
+#pragma unroll
+        for (int u = 0; u < DA_BATCH; ++u) {
+            jj[u] = w.j; ii[u] = w.i; w.next();
+            raw[u] = (jj[u] < n && ii[u] < nv) ? S0[(size_t)jj[u] * nv + ii[u]] : 0.0f;
+        }
+#pragma unroll
+        for (int u = 0; u < DA_BATCH; ++u)
+            if (jj[u] < np) Ss[jj[u] * nvp + ii[u]] = raw[u];
     }
     __syncthreads();
     // scores of the chunk's own tokens: a 4 x 4 tile (queries t0.., keys j0..) per thread
@@ -402,11 +457,11 @@ extern "C" int bg_decay_attention_chunked(const void* src, int src_dtype, int sr
             cudaError_t e = cudaFuncSetAttribute(kout, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_out);
             if (e != cudaSuccess) return (int)e;
         }
-        launch(ksum, dim3(H, n_chunks), dim3(256), smem_sum, stream, p);
+        launch(ksum, dim3(H, n_chunks), dim3(DC_THREADS), smem_sum, stream, p);
         BG_LAUNCH_CHECK();
         launch(decay_chunk_scan_kernel, dim3((n * nv + 255) / 256, H, n_long), dim3(256), 0, stream, p);
         BG_LAUNCH_CHECK();
-        launch(kout, dim3(H, n_chunks), dim3(256), smem_out, stream, p);
+        launch(kout, dim3(H, n_chunks), dim3(DC_THREADS), smem_out, stream, p);
     });
     BG_LAUNCH_CHECK();
     return BG_OK;
