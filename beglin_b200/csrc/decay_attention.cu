@@ -4,9 +4,11 @@
 //     S <- d S + k v^T        (S is n x nv, float, one per request and head, zero when the request starts)
 //     o  = S^T q
 // The state is carried from step to step in a slot of the cache manager's slab.  Everything is float: the state, the
-// decay, the products that enter it and the readout.  Two kernels:
-//   decay_attention_seq_kernel    one block per (head, request) walks the request's tokens in turn, the state in shared
-//                                 memory.  For steps of single tokens and short portions, and for any sizes.
+// decay, the products that enter it and the readout.  Three kernels:
+//   decay_attention_reg_kernel    blocks per (head, request, 32 columns of the state) walk the request's tokens in turn,
+//                                 the state in registers.  For steps of single tokens and short portions.
+//   decay_attention_seq_kernel    the same walk with a head's whole state in shared memory, one block per (head,
+//                                 request): for heads of more rows than the registers take.
 //   decay_attention_chunk_*       long portions, cut into chunks of DC tokens: the chunks' own sums of decayed k v^T in
 //                                 parallel, a short pass over the chunks that turns them into the states at the chunks'
 //                                 starts, then every chunk's outputs in parallel (the earlier chunks through the state,
@@ -80,6 +82,76 @@ __global__ void __launch_bounds__(256) decay_attention_seq_kernel(DecayAttnParam
     }
     __syncthreads();
     for (int i = tid; i < n * nv; i += blockDim.x) st[i] = S[i];
+}
+
+// The same walk with the state in registers: a block takes DA_COLS columns of one head's state (of one request), thread
+// (slice, column) holds the rows slice, slice + slices, ... of its column, at most R of them.  A head of nv columns is
+// spread over nv / DA_COLS blocks, which share nothing: a column's sum over the rows stays inside its block.
+constexpr int DA_COLS = 32;
+
+template <typename TS, int R>
+__global__ void __launch_bounds__(256) decay_attention_reg_kernel(DecayAttnParams p) {
+    extern __shared__ float da_s[];
+    const int n = p.n, nv = p.nv;
+    const int cols = nv < DA_COLS ? nv : DA_COLS;
+    const int slices = (int)blockDim.x / cols;
+    float* qs = da_s;                      // [n]
+    float* ks = qs + n;                    // [n]
+    float* vs = ks + n;                    // [cols]
+    float* red = vs + cols;                // [slices][cols]
+    pdl_launch();
+    const int h = blockIdx.x, r = blockIdx.y, col0 = blockIdx.z * cols;
+    const int req = p.reqs[r * 3 + 0], row0 = p.reqs[r * 3 + 1], rows = p.reqs[r * 3 + 2];
+    const int tid = threadIdx.x;
+    const int sl = tid / cols, c = tid - sl * cols;
+    const bool own = sl < slices && col0 + c < nv;
+    const float d = p.decay[h];
+    pdl_wait();
+    if (rows <= 0) return;
+    float* st = p.state + (size_t)p.slots[req] * p.slot_stride + (size_t)h * n * nv + col0 + c;
+    float S[R];
+#pragma unroll
+    for (int k = 0; k < R; ++k) {
+        const int i = sl + k * slices;
+        S[k] = (own && i < n) ? st[(size_t)i * nv] : 0.0f;
+    }
+    const TS* src = (const TS*)p.src;
+    for (int t = 0; t < rows; ++t) {
+        const TS* row = src + (size_t)(row0 + t) * p.src_stride;
+        __syncthreads();
+        for (int i = tid; i < n; i += blockDim.x) {
+            qs[i] = da_silu(sum_parts(row + p.q_col + h * n + i, p.parts, p.part_stride));
+            ks[i] = da_silu(sum_parts(row + p.k_col + h * n + i, p.parts, p.part_stride));
+        }
+        if (tid < cols && col0 + tid < nv) vs[tid] = da_silu(sum_parts(row + p.v_col + h * nv + col0 + tid, p.parts, p.part_stride));
+        __syncthreads();
+        if (own) {
+            const float v = vs[c];
+            float acc = 0.0f;
+#pragma unroll
+            for (int k = 0; k < R; ++k) {
+                const int i = sl + k * slices;
+                if (i < n) {
+                    S[k] = fmaf(d, S[k], ks[i] * v);
+                    acc = fmaf(S[k], qs[i], acc);
+                }
+            }
+            red[sl * cols + c] = acc;
+        }
+        __syncthreads();
+        if (tid < cols && col0 + tid < nv) {
+            float acc = 0.0f;
+            for (int q = 0; q < slices; ++q) acc += red[q * cols + tid];
+            p.y[(size_t)(row0 + t) * p.H * nv + (size_t)h * nv + col0 + tid] = acc;
+        }
+    }
+    if (own) {
+#pragma unroll
+        for (int k = 0; k < R; ++k) {
+            const int i = sl + k * slices;
+            if (i < n) st[(size_t)i * nv] = S[k];
+        }
+    }
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -407,6 +479,18 @@ extern "C" int bg_decay_attention(const void* src, int src_dtype, int src_stride
     p.v_col = v_col; p.decay = decay; p.state = state; p.slot_stride = (size_t)slot_stride; p.slots = slots; p.reqs = reqs; p.y = y;
     p.H = H; p.n = n; p.nv = nv;
     const int threads = 256;
+    // the state in registers where a thread's share of a column fits (heads of up to 256 rows), else in shared memory
+    const int cols = nv < DA_COLS ? nv : DA_COLS, rslices = threads / cols, per_thread = (n + rslices - 1) / rslices;
+    if (per_thread <= 32 && (nv + cols - 1) / cols <= 65535) {
+        const size_t rsmem = ((size_t)2 * n + cols + (size_t)rslices * cols) * sizeof(float);
+        const dim3 grid(H, n_req, (nv + cols - 1) / cols);
+        BG_DISPATCH_DTYPE(src_dtype, TS, {
+            if (per_thread <= 16) launch(decay_attention_reg_kernel<TS, 16>, grid, dim3(threads), rsmem, stream, p);
+            else launch(decay_attention_reg_kernel<TS, 32>, grid, dim3(threads), rsmem, stream, p);
+        });
+        BG_LAUNCH_CHECK();
+        return BG_OK;
+    }
     const int slices = nv <= threads ? threads / nv : 1;
     const size_t smem = ((size_t)n * nv + 2 * n + nv + (size_t)slices * nv) * sizeof(float);
     if (smem > 200 * 1024) return BG_ERR_UNSUPPORTED;

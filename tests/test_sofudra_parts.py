@@ -49,7 +49,8 @@ def run_decayed(src, H, n, nv, decay, state, slots, lens, chunked, extra=3):
     chunk = o.decay_attention_chunk(n, nv)
     dev = lambda a: torch.from_numpy(a).to(DEV)
     if chunked:
-        assert chunk > 0
+        if chunk == 0:
+            pytest.skip("heads of this size run token by token only")
         short, blocks, longs = cut_long_requests(starts, lens, chunk, 16)
         o.decay_attention(src, 0, H * n, 2 * H * n, decay, state, slots, dev(short), short.shape[0], y, H, n, nv,
                           dev(blocks), blocks.shape[0], dev(longs), longs.shape[0])
@@ -59,7 +60,8 @@ def run_decayed(src, H, n, nv, decay, state, slots, lens, chunked, extra=3):
     return y
 
 
-@pytest.mark.parametrize("H,n,nv", [(1, 1, 1), (3, 6, 10), (2, 14, 5), (4, 32, 32), (2, 64, 64), (1, 128, 128), (2, 33, 7), (1, 96, 40)])
+@pytest.mark.parametrize("H,n,nv", [(1, 1, 1), (3, 6, 10), (2, 14, 5), (4, 32, 32), (2, 64, 64), (1, 128, 128), (2, 33, 7), (1, 96, 40), (1, 300, 40),
+                                    (2, 200, 3)])
 @pytest.mark.parametrize("chunked", [False, True])
 @pytest.mark.parametrize("parts", [1, 3])
 def test_decayed_state(H, n, nv, chunked, parts):
