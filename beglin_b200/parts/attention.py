@@ -117,6 +117,11 @@ class GQAAttention:
         if b is not None and spec.gate:                # the gate's rows of the one product have no bias
             b = torch.cat([b, torch.zeros(tensors["g_proj.weight"].shape[0], dtype=b.dtype, device=b.device)])
         self.gate_col = self.qd + (self.kvd + self.nkv * self.vd if spec.own_kv else 0)
+        pad = (-w.shape[0]) % 8
+        if spec.gate == "head" and pad:                # one gate per head: rows of zeros behind them keep the product's
+            w = torch.cat([w, torch.zeros((pad, w.shape[1]), dtype=w.dtype, device=w.device)], dim=0)       # rows 16 bytes apart
+            if b is not None:
+                b = torch.cat([b, torch.zeros(pad, dtype=b.dtype, device=b.device)])
         f32 = lambda t: t.to(device=ctx.device, dtype=torch.float32).contiguous()
         self.q_norm = f32(tensors["q_norm.weight"]) if spec.qk_norm else None
         self.k_norm = f32(tensors["k_norm.weight"]) if spec.qk_norm else None
