@@ -482,12 +482,14 @@ __global__ void __launch_bounds__(256) add_terms_norm_vec4_kernel(TermsParams p)
             const float sc = p.scale[i];
             if (p.dtype[i] == BG_DTYPE_F32) {
                 const float* base = (const float*)p.term[i] + at;
+#pragma unroll 4
                 for (int q = 0; q < p.parts[i]; ++q) {
                     const float4 a = *reinterpret_cast<const float4*>(base + (size_t)q * p.part_stride[i]);
                     v.x = fmaf(sc, a.x, v.x); v.y = fmaf(sc, a.y, v.y); v.z = fmaf(sc, a.z, v.z); v.w = fmaf(sc, a.w, v.w);
                 }
             } else {
                 const __nv_bfloat16* base = (const __nv_bfloat16*)p.term[i] + at;
+#pragma unroll 4
                 for (int q = 0; q < p.parts[i]; ++q) {
                     const uint2 raw = *reinterpret_cast<const uint2*>(base + (size_t)q * p.part_stride[i]);
                     const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
