@@ -388,15 +388,15 @@ def nadilorn_config(width, heads, layers, vocab=32768, vdim=128):
 # The Sofudra decoder beside another design at equal layer sizes (--design sofudra): a first layer of grouped-query
 # attention with heads of 128 features normed one by one, whole heads rotated with stretched frequencies, a window of
 # 1,024 positions and a learned sink; then layers of two mixers side by side (attention without rotation, scores squashed
-# at 30, one gate per head; beside it linear attention with a constant decay per head, width / 128 heads of 128 x 128
+# at 50, one gate per head; beside it linear attention with a constant decay per head, width / 128 heads of 128 x 128
 # values of state), every layer with a dense GELU feed-forward of the Qwen2 layer's weights (two matrices of 3/2 its inner
 # size) read from the same stream as the mixer.  Two of the layers are passed twice with the input mix in front, so that
 # the number of layer runs is the other model's number of layers.  Random weights.
 def sofudra_config(width, heads, layers, vocab=32768):
     kv = max(1, heads // 4 if heads % 4 == 0 and heads > 12 else heads // 6)
     first = {"heads": heads, "kv_heads": kv, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": 1024},
-             "rot": {"base": 500000.0, "dims": 128, "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}}}
-    left = {"heads": heads, "kv_heads": kv, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 30.0}
+             "rot": {"base": 1000000.0, "dims": 128, "scaling": {"factor": 4.0, "original": 4096, "fast": 16.0, "slow": 2.0}}}
+    left = {"heads": heads, "kv_heads": kv, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 50.0}
     dh = width // 128
     right = {"heads": dh, "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** (-3.0 - 5.0 * i / max(1, dh - 1)) for i in range(dh)]}
     ff = {"kind": "dense", "ff": (4 * width) // 128 * 128}

@@ -76,10 +76,10 @@ SHARP = config(150, 64, 1e-5, [
 # sizes in multiples of 64: in bfloat16 the products run this package's tensor-core kernels; no loop
 EVEN = config(320, 128, 1e-5, [
     layer(attn(4, 2, 64, 64, 0.125, window=80, rot=32, base=10000.0, scaling=(4.0, 256, 16.0, 2.0)), 256),
-    layer(par(gated(4, 1, 64, 32, 0.125, 30.0), decayed(2, 64, 64, [0.9, 0.995]), 1.1, 0.9), 192),
+    layer(par(gated(4, 1, 64, 32, 0.125, 20.0), decayed(2, 64, 64, [0.9, 0.995]), 1.1, 0.9), 192),
     layer(par(gated(2, 2, 128, 128, 0.09, 10.0), decayed(4, 32, 16, [0.6, 0.8, 0.95, 0.99]), 0.8, 1.2), 128),
     layer(attn(8, 2, 32, 64, 0.18, window=200, rot=16, base=1000.0)),
-], embed_scale=8.0, mult=0.3, cap=12.0)
+], embed_scale=8.0, mult=0.35, cap=12.0)
 CONFIGS = {"odd": (ODD, 8), "sharp": (SHARP, 16), "even": (EVEN, 16)}        # name -> (config, page size)
 
 

@@ -35,8 +35,8 @@ def random_config(case: int, even: bool = False):
         scale = rng.uniform(0.3, 2.0) / dim ** 0.5
         if rng.random() < 0.5:
             rot = rng.choice([dim, 2 * rng.randrange(1, dim // 2 + 1)])
-            scaling = rng.choice([None, (rng.choice([1.0, 2.0, 3.7, 8.0]), rng.choice([16, 64, 1024]),
-                                         rng.choice([32.0, 4.0]), rng.choice([1.0, 0.5, 2.0]))])
+            scaling = rng.choice([None, (rng.choice([1.0, 2.0, 3.7, 6.0]), rng.choice([16, 64, 512]),
+                                         rng.choice([24.0, 4.0]), rng.choice([1.0, 0.5, 2.0]))])
             mixer = attn(heads, kv, dim, vdim, scale, window=rng.choice([1, 2, rng.randrange(3, 20), rng.randrange(20, 200)]),
                          rot=rot, base=rng.choice([10.0, 1000.0, 5e5]), scaling=scaling)
         else:
