@@ -467,7 +467,7 @@ __global__ void __launch_bounds__(256) add_terms_norm_kernel(TermsParams p) {
 
 // The same, four columns a thread at a time (d a multiple of 4, every pointer 16-byte aligned): the terms are walked
 // outside the columns, so a term's type and its number of partial sums are looked at once per group of four.
-__global__ void __launch_bounds__(256) add_terms_norm_vec4_kernel(TermsParams p) {
+__global__ void __launch_bounds__(1024) add_terms_norm_vec4_kernel(TermsParams p) {
     extern __shared__ __align__(16) float row_s[];
     __shared__ float red[32];
     pdl_launch();
@@ -640,7 +640,9 @@ extern "C" int bg_add_terms_norm(float* x, int n_rows, int d, int assign, int n_
     bool vec = d % 4 == 0 && ((uintptr_t)x % 16) == 0 && (!out1 || (uintptr_t)out1 % 16 == 0) && (!out2 || (uintptr_t)out2 % 16 == 0);
     for (int i = 0; i < n_terms; ++i)
         vec = vec && ((uintptr_t)terms[i] % 16) == 0 && (part_strides[i] % 4) == 0;
-    if (vec) launch(add_terms_norm_vec4_kernel, dim3(n_rows), dim3(256), smem, stream, p);
+    // steps of few rows cannot fill the device with rows: a row's groups of four columns then get a thread each
+    const int vthreads = n_rows >= 512 ? 256 : (d / 4 + 31) / 32 * 32 < 64 ? 64 : (d / 4 + 31) / 32 * 32 > 1024 ? 1024 : (d / 4 + 31) / 32 * 32;
+    if (vec) launch(add_terms_norm_vec4_kernel, dim3(n_rows), dim3(vthreads), smem, stream, p);
     else launch(add_terms_norm_kernel, dim3(n_rows), dim3(256), smem, stream, p);
     BG_LAUNCH_CHECK();
     return BG_OK;
