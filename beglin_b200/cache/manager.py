@@ -11,7 +11,8 @@ Stages of the model whose mixers have equal needs form a group.  A group of page
 has one pool of pages (shared by its stages: page p of every stage of the group belongs to the same
 request and the same positions) and one block table per request.  What a page holds is the need's
 business (`page_shape`): keys and values per kv head, or one latent row per position.  A group with a window gives back
-the pages that lie wholly behind the window as a request advances.  A group of fixed state has one
+the pages that lie wholly behind the window as a request advances (one whose queries read their own block of positions
+only, the pages in front of the newest block).  A group of fixed state has one
 slab [stages, slots, ...]; a request's slot is zeroed when the request starts.  A stage whose mixer is made of
 branches (attention beside a recurrence) hands in a composite need: each of its needs joins the group of its kind,
 and the stage's view is the tuple of the branches' views.
@@ -85,10 +86,17 @@ class _KVGroup:
         self.device_pool: Optional[torch.Tensor] = None  # [stages, pages, *need.page_shape]: [.., 2, nkv, page, hd] or [.., page, width]
 
     def first_needed_page(self, first_query_pos: int, page_size: int) -> int:
-        if self.need.window is None:
-            return 0
-        lo = max(0, first_query_pos - self.need.window + 1)
+        lo = 0
+        if self.need.window is not None:
+            lo = max(lo, first_query_pos - self.need.window + 1)
+        if self.need.block is not None:                # a query reads its own block of positions only
+            lo = max(lo, first_query_pos - first_query_pos % self.need.block)
         return lo // page_size
+
+    @property
+    def gives_back(self) -> bool:
+        """Whether pages are returned while a request still grows."""
+        return self.need.window is not None or self.need.block is not None
 
 
 class _StateGroup:
@@ -253,7 +261,7 @@ class CacheManager:
         """For every group, the (give back, add) of every entry of the plan."""
         out, ps = [], self.page_size
         for g in self.kv_groups:
-            if g.need.window is None:          # nothing is ever given back before the request ends
+            if not g.gives_back:               # nothing is ever given back before the request ends
                 tables = g.tables
                 out.append([((), max(0, -(-new_len // ps) - len(tables[rid]))) for rid, new_len in plan])
             else:

@@ -8,7 +8,8 @@
 // them as a partial result; `attention_merge` joins the partials of a row in split order.
 //
 // The math of one (row, head) is that of qwen_infer.c:1538-1543: s_t = (q . K_t) * scale for the
-// visible t (t <= position, and t > position - window when there is a window), softmax with the
+// visible t (t <= position, and t >= first_visible(position, window): a sliding window, or the query's own block of
+// positions), softmax with the
 // maximum subtracted, o = sum_t p_t V_t.  Everything is float.  Because tiles and splits start at
 // absolute positions and a row never shares an accumulator with another row, the result of a row
 // does not depend on how the step was cut or on what else is in the batch.
@@ -73,7 +74,7 @@ attention_partial_kernel(AttnParams p) {
     if (nq <= 0) return;
     const int pos_first = p.positions[row0];
     const int pos_last = p.positions[row0 + nq - 1];
-    const int lo_first = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
+    const int lo_first = first_visible(pos_first, p.window);
     const int k_begin = max(sp * p.split, lo_first);
     const int k_end = min((sp + 1) * p.split, pos_last + 1);       // exclusive
     if (k_begin >= k_end) return;
@@ -129,7 +130,7 @@ attention_partial_kernel(AttnParams p) {
         for (int r = warp; r < n_rows; r += ATT_WARPS) {
             const int qi = r / group;
             const int pos = p.positions[row0 + qi];
-            const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+            const int lo = first_visible(pos, p.window);
             const float* qr = q_s + (size_t)r * hd;
             float s[2];
             float tmax = -INFINITY;
@@ -196,7 +197,7 @@ attention_partial_kernel(AttnParams p) {
     for (int r = warp; r < n_rows; r += ATT_WARPS) {
         const int qi = r / group, g = r - qi * group;
         const int pos = p.positions[row0 + qi];
-        const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+        const int lo = first_visible(pos, p.window);
         if (pos < sp * p.split || lo >= (sp + 1) * p.split) continue;
         const size_t prow = ((size_t)(row0 + qi) * p.nh + (size_t)kvh * group + g) * p.max_splits + sp;
         for (int d = lane; d < vd; d += 32) p.part_o[prow * vd + d] = acc_s[(size_t)r * vd + d];
@@ -223,7 +224,7 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o, const f
     const int t = w / nh, h = w - t * nh;
     const int pos = positions[t];
     const int split = keys_per_split(split_arg, pos + 1, max_splits);
-    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int lo = first_visible(pos, window);
     const int s_lo = lo / split, s_hi = pos / split;
     const size_t prow = (size_t)w * max_splits;
     // the maxima and sums of the first 32 * MERGE_GROUPS splits of the row: lane j holds split s_lo + 32 g + j
@@ -367,7 +368,7 @@ __global__ void attention_merge_few_kernel(const float* __restrict__ part_o, con
     // worked out while the kernel ahead still runs
     const int pos = positions[t];
     const int split = keys_per_split(split_arg, pos + 1, max_splits);
-    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int lo = first_visible(pos, window);
     const int s_lo = lo / split, s_hi = pos / split;
     pdl_wait();
     if (idle) return;                  // (not before the wait: with warps of a CTA gone before it, rows came out wrong)
@@ -432,7 +433,7 @@ attention_merge_block_kernel(const float* __restrict__ part_o, const float* __re
     // (the row's position is written by no kernel of the step: its range of splits is worked out before the wait)
     const int pos = positions[t];
     const int split = keys_per_split(split_arg, pos + 1, max_splits);
-    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int lo = first_visible(pos, window);
     const int s_lo = lo / split, s_hi = pos / split;
     pdl_wait();
     const size_t prow = (size_t)w * max_splits;

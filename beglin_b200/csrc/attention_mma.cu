@@ -180,7 +180,7 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_co
         table_s[i] = pi < p.max_pages ? p.block_table[(size_t)req * p.max_pages + pi] : -1;
     }
 
-    const int lo_first = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
+    const int lo_first = first_visible(pos_first, p.window);
     const int k_begin = direct ? lo_first : max(sp * split, lo_first);
     const int k_end = direct ? pos_last + 1 : min((sp + 1) * split, pos_last + 1);
     if (k_begin >= k_end) return;
@@ -324,7 +324,7 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_co
         int r = row_base + (lane >> 2) + h * 8;
         if (r < n_rows) {
             pos_r[h] = pos_first + r / group;
-            lo_r[h] = p.window > 0 ? max(0, pos_r[h] - p.window + 1) : 0;
+            lo_r[h] = first_visible(pos_r[h], p.window);
         } else {
             pos_r[h] = -1; lo_r[h] = 0;
         }
@@ -333,8 +333,8 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_co
     const int warp_row_hi = min(n_rows - 1, row_base + 15);
     const int warp_pos_hi = row_base < n_rows ? pos_first + warp_row_hi / group : -1;
     const int warp_pos_lo = pos_first + min(row_base, n_rows - 1) / group;
-    const int warp_lo = p.window > 0 ? max(0, warp_pos_lo - p.window + 1) : 0;
-    const int warp_lo_hi = p.window > 0 ? max(0, warp_pos_hi - p.window + 1) : 0;
+    const int warp_lo = first_visible(warp_pos_lo, p.window);
+    const int warp_lo_hi = first_visible(warp_pos_hi, p.window);
     // byte offsets inside a 16-key block that do not change from block to block: the XOR of the swizzle
     // depends on the row's low three bits, which for a given lane are the same in every block
     int koff[KSTEPS], voff[NT_O / 2];
@@ -444,7 +444,7 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_co
                 }
             }
             const int r0 = 2 * (lane & 3);
-            const int pos = pos_first, lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+            const int pos = pos_first, lo = first_visible(pos, p.window);
             const bool all_seen = w_key0 >= k_begin && w_key0 + 16 * KB <= k_end && w_key0 >= lo && w_key0 + 16 * KB - 1 <= pos;
             float tmax[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -660,7 +660,7 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_co
         }
         compute_sync();
         const int pos = pos_first;
-        const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+        const int lo = first_visible(pos, p.window);
         if (!(pos < sp * split || lo >= (sp + 1) * split)) {
             // every thread takes one feature of all rows and works out the weights of the four warps' parts itself
             // (four exponentials a row: cheaper than a third barrier and a round through shared memory)

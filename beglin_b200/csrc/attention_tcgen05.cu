@@ -146,7 +146,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
     const int n_rows = nq * group;                       // <= 128
     const int pos_first = p.positions[row0];
     const int pos_last = pos_first + nq - 1;
-    const int k_begin = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
+    const int k_begin = first_visible(pos_first, p.window);
     const int k_end = pos_last + 1;
     const int tile0 = k_begin / AT_BK;
     const int n_tiles = (k_end + AT_BK - 1) / AT_BK - tile0;
@@ -264,7 +264,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
         const unsigned lane_addr = (unsigned)(quarter * 32) << 16;
         const bool real = r < n_rows;
         const int pos = real ? pos_first + r / group : -1;
-        const int lo = (real && p.window > 0) ? max(0, pos - p.window + 1) : 0;
+        const int lo = real ? first_visible(pos, p.window) : 0;
         const int warp_pos_min = __reduce_min_sync(0xffffffffu, real ? pos : 0x7fffffff);
         const int warp_lo_max = __reduce_max_sync(0xffffffffu, lo);
         float m = -INFINITY, l = 0.0f;
@@ -531,7 +531,8 @@ static int attention_tc(const void* q, int q_stride, const void* kv_pool, int nu
     int rc = pt_pool_map(&map, kv_pool, num_pages, nkv, page_size, hd);
     if (rc != BG_OK) return rc;
     // tiles of 128 keys where a block may walk many of them (max_position bounds the positions of the step's rows)
-    const bool wide = (window > 0 ? (window < max_position + 1 ? window : max_position + 1) : max_position + 1) >= at_wide_from();
+    const int reach = window != 0 ? abs(window) : max_position + 1;          // the most keys a row can see
+    const bool wide = (reach < max_position + 1 ? reach : max_position + 1) >= at_wide_from();
     if (sink) {
         if (hd == 128) return wide ? at_launch<128, 128, true>(map, p, n_qblk, stream) : at_launch<128, 64, true>(map, p, n_qblk, stream);
         return wide ? at_launch<64, 128, true>(map, p, n_qblk, stream) : at_launch<64, 64, true>(map, p, n_qblk, stream);

@@ -111,6 +111,15 @@ __host__ __device__ __forceinline__ int keys_per_split(int split, int n_keys, in
     return r < 256 ? 256 : r;
 }
 
+// The first position that a query at `pos` sees.  window > 0: itself and the window - 1 positions before it.  window < 0:
+// the positions of its own block of -window positions, blocks counted from position 0 of the sequence (a query never
+// looks across a block's start).  0: every position up to its own.  The bound never falls as `pos` grows.
+__host__ __device__ __forceinline__ int first_visible(int pos, int window) {
+    if (window > 0) return pos - window + 1 > 0 ? pos - window + 1 : 0;
+    if (window < 0) return pos - pos % (-window);
+    return 0;
+}
+
 template <typename T> __device__ __forceinline__ float to_float(T v);
 template <> __device__ __forceinline__ float to_float<float>(float v) { return v; }
 template <> __device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }

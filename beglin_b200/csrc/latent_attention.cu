@@ -95,6 +95,7 @@ struct LatentParams {
     int H, hc;              // heads, heads per CTA
     int rank, rot, rot_dims;
     int split, tile, bq;
+    int window;             // as first_visible() reads it; 0: every earlier position
     float scale;
     unsigned* status;
 };
@@ -122,7 +123,9 @@ latent_attention_partial_kernel(LatentParams p) {
     const int h0 = hchunk * p.hc;
     const int nh = min(p.hc, p.H - h0);
     const int pos_last = p.positions[row0 + nq - 1];
-    const int k_begin = sp * p.split;
+    const int lo_first = first_visible(p.positions[row0], p.window);
+    // the first tile that holds a key any row sees (tiles start at multiples of `tile`, as split does)
+    const int k_begin = max(sp * p.split, (lo_first / p.tile) * p.tile);
     const int k_end = min((sp + 1) * p.split, pos_last + 1);       // exclusive
     if (k_begin >= k_end) return;
 
@@ -197,6 +200,7 @@ latent_attention_partial_kernel(LatentParams p) {
         for (int r = warp; r < n_rows; r += LAT_WARPS) {
             const int qi = r / nh;
             const int pos = p.positions[row0 + qi];
+            const int lo = first_visible(pos, p.window);
             const float* qrow = q_s + (size_t)r * width;
             float s[2];
             float tmax = -INFINITY;
@@ -206,7 +210,7 @@ latent_attention_partial_kernel(LatentParams p) {
                 const int j = c * 32 + lane;
                 if (j < tile) {
                     const int key = t0 + j;
-                    if (key <= pos && key < k_end && base_s[j] >= 0) {
+                    if (key >= lo && key <= pos && key < k_end && base_s[j] >= 0) {
                         const float* kr = k_s + j * kstride;
                         float d0 = 0.0f, d1 = 0.0f, d2 = 0.0f, d3 = 0.0f;      // four chains, joined in a fixed order
                         int d = 0;
@@ -261,14 +265,14 @@ latent_attention_partial_kernel(LatentParams p) {
     for (int r = warp; r < n_rows; r += LAT_WARPS) {
         const int qi = r / nh, g = r - qi * nh;
         const int pos = p.positions[row0 + qi];
-        if (pos < k_begin) continue;
+        if (pos < sp * p.split || first_visible(pos, p.window) >= (sp + 1) * p.split) continue;
         const size_t prow = ((size_t)(row0 + qi) * p.H + h0 + g) * p.max_splits + sp;
         for (int d = lane; d < rank; d += 32) p.part_o[prow * rank + d] = acc_s[(size_t)r * rank + d];
         if (lane == 0) { p.part_ml[prow * 2 + 0] = m_s[r]; p.part_ml[prow * 2 + 1] = l_s[r]; }
     }
 }
 
-// out[h][t][:] = sum_s o_s e^(m_s - m) / sum_s l_s e^(m_s - m) over the splits 0 .. position / split, in split
+// out[h][t][:] = sum_s o_s e^(m_s - m) / sum_s l_s e^(m_s - m) over the splits that hold a key the row sees, in split
 // order.  One block of 128 threads per (row, head): the splits' weights are worked out once, by the first warp, and
 // every thread then sums its features over the splits with all its loads independent of one another (a warp per
 // (row, head) that recomputed the weights for every 32 features took 32 us for 96 rows of 17 splits).
@@ -277,29 +281,30 @@ template <typename TO>
 __global__ void __launch_bounds__(LAT_MERGE_THREADS)
 latent_attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                               const int* __restrict__ positions, TO* __restrict__ out, long long out_head,
-                              int out_row, int T, int H, int rank, int max_splits, int split) {
+                              int out_row, int T, int H, int rank, int max_splits, int split, int window) {
     extern __shared__ float f_s[];                 // [max_splits] weights e^(m_s - m) / l
     pdl_launch();
     pdl_wait();
     const int w = blockIdx.x;
     const int t = w / H, h = w - t * H;
     const int s_hi = positions[t] / split;
+    const int s_lo = first_visible(positions[t], window) / split;
     const size_t prow = (size_t)w * max_splits;
     const int lane = threadIdx.x & 31;
     if (threadIdx.x < 32) {
         float m = -INFINITY;
-        for (int s = lane; s <= s_hi; s += 32) m = fmaxf(m, part_ml[(prow + s) * 2]);
+        for (int s = s_lo + lane; s <= s_hi; s += 32) m = fmaxf(m, part_ml[(prow + s) * 2]);
         m = warp_max(m);
         float l = 0.0f;
-        for (int s = 0; s <= s_hi; ++s) l = fmaf(part_ml[(prow + s) * 2 + 1], expf(part_ml[(prow + s) * 2] - m), l);
+        for (int s = s_lo; s <= s_hi; ++s) l = fmaf(part_ml[(prow + s) * 2 + 1], expf(part_ml[(prow + s) * 2] - m), l);
         const float inv = 1.0f / l;
-        for (int s = lane; s <= s_hi; s += 32) f_s[s] = expf(part_ml[(prow + s) * 2] - m) * inv;
+        for (int s = s_lo + lane; s <= s_hi; s += 32) f_s[s] = expf(part_ml[(prow + s) * 2] - m) * inv;
     }
     __syncthreads();
     TO* o = out + (size_t)h * out_head + (size_t)t * out_row;
     for (int d = threadIdx.x; d < rank; d += LAT_MERGE_THREADS) {
         float acc = 0.0f;
-        for (int s = 0; s <= s_hi; ++s) acc = fmaf(part_o[(prow + s) * rank + d], f_s[s], acc);
+        for (int s = s_lo; s <= s_hi; ++s) acc = fmaf(part_o[(prow + s) * rank + d], f_s[s], acc);
         o[d] = from_float<TO>(acc);
     }
 }
@@ -312,19 +317,20 @@ latent_attention_merge_kernel(const float* __restrict__ part_o, const float* __r
 // small kernels: the request's cached rows gathered into a matrix, the per-head rows put into pages (keys with the
 // shared rotated part behind them), and the rotation of the queries' rot part in place.
 
-// lat[s, :] and kr[s, :] = the latent and the rotated key part of the cached row of position s of request `req`,
+// lat[s, :] and kr[s, :] = the latent and the rotated key part of the cached row of position first + s of request `req`,
 // zeros where the block table holds no page.  Two matrices, so that the product that follows reads a dense one.
 __global__ void latent_gather_kernel(const __nv_bfloat16* __restrict__ pool, const int* __restrict__ block_table, int max_pages,
-                                     int req, int num_pages, int page_size, int rank, int rot, int S,
+                                     int req, int num_pages, int page_size, int rank, int rot, int S, int first,
                                      __nv_bfloat16* __restrict__ lat, __nv_bfloat16* __restrict__ kr) {
     pdl_launch();
     pdl_wait();
     const int s = blockIdx.x;
     if (s >= S) return;
     const int width = rank + rot;
-    const int page = block_table[(size_t)req * max_pages + s / page_size];
+    const int at = first + s;                                  // the position whose row this is
+    const int page = at / page_size < max_pages ? block_table[(size_t)req * max_pages + at / page_size] : -1;
     const bool ok = page >= 0 && page < num_pages;
-    const __nv_bfloat16* src = pool + ((size_t)(ok ? page : 0) * page_size + s % page_size) * width;
+    const __nv_bfloat16* src = pool + ((size_t)(ok ? page : 0) * page_size + at % page_size) * width;
     const __nv_bfloat16 zero = __float2bfloat16_rn(0.0f);
     if ((width & 7) == 0 && (rank & 7) == 0) {                 // rows and both parts on 16-byte boundaries
         for (int c = threadIdx.x; c < width / 8; c += blockDim.x) {
@@ -429,7 +435,7 @@ extern "C" int bg_latent_attention_partial(const void* q_lat, int ql_dtype, long
                                            const int* block_table, int max_pages, const int* positions, const int* qblk,
                                            int n_qblk, float* part_o, float* part_ml, int max_splits, int n_splits_launch,
                                            int H, int hc, int rank, int rot, int rot_dims, int split, int tile, int bq,
-                                           float scale, unsigned* status, cudaStream_t stream) {
+                                           int window, float scale, unsigned* status, cudaStream_t stream) {
     if (n_qblk <= 0 || n_splits_launch <= 0) return BG_OK;
     if (H <= 0 || hc <= 0 || hc > H || rank <= 0 || rot < 0 || rot_dims > rot || (rot_dims & 1)) return BG_ERR_SHAPE;
     if ((tile != 32 && tile != 64) || split % tile != 0 || bq <= 0) return BG_ERR_SHAPE;
@@ -440,7 +446,7 @@ extern "C" int bg_latent_attention_partial(const void* q_lat, int ql_dtype, long
     p.qr_off = qr_off; p.cos_sin = cos_sin; p.pool = pool; p.num_pages = num_pages; p.page_size = page_size;
     p.block_table = block_table; p.max_pages = max_pages; p.positions = positions; p.qblk = qblk; p.part_o = part_o;
     p.part_ml = part_ml; p.max_splits = max_splits; p.H = H; p.hc = hc; p.rank = rank; p.rot = rot; p.rot_dims = rot_dims;
-    p.split = split; p.tile = tile; p.bq = bq; p.scale = scale; p.status = status;
+    p.split = split; p.tile = tile; p.bq = bq; p.window = window; p.scale = scale; p.status = status;
     const size_t smem = latent_smem_bytes(bq * hc, rank, rot, tile);
     if (smem > 227 * 1024) return BG_ERR_UNSUPPORTED;
     dim3 grid(n_qblk, chunks, n_splits_launch);
@@ -464,22 +470,22 @@ extern "C" int bg_latent_attention_partial(const void* q_lat, int ql_dtype, long
 
 extern "C" int bg_latent_attention_merge(const float* part_o, const float* part_ml, const int* positions, void* out,
                                          int out_dtype, long long out_head, int out_row, int T, int H, int rank,
-                                         int max_splits, int split, cudaStream_t stream) {
+                                         int max_splits, int split, int window, cudaStream_t stream) {
     const long long blocks = (long long)T * H;
     if (blocks <= 0) return BG_OK;
     if (blocks > 0x7fffffffLL || max_splits > 8192) return BG_ERR_SHAPE;
     BG_DISPATCH_DTYPE(out_dtype, TO,
         launch(latent_attention_merge_kernel<TO>, dim3((unsigned)blocks), dim3(LAT_MERGE_THREADS), (size_t)max_splits * sizeof(float),
-               stream, part_o, part_ml, positions, (TO*)out, out_head, out_row, T, H, rank, max_splits, split));
+               stream, part_o, part_ml, positions, (TO*)out, out_head, out_row, T, H, rank, max_splits, split, window));
     BG_LAUNCH_CHECK();
     return BG_OK;
 }
 
 extern "C" int bg_latent_gather(const void* pool, const int* block_table, int max_pages, int req, int num_pages, int page_size,
-                                int rank, int rot, int S, void* lat, void* kr, cudaStream_t stream) {
+                                int rank, int rot, int S, int first, void* lat, void* kr, cudaStream_t stream) {
     if (S <= 0) return BG_OK;
     launch(latent_gather_kernel, dim3(S), dim3(64), 0, stream, (const __nv_bfloat16*)pool, block_table, max_pages, req, num_pages,
-           page_size, rank, rot, S, (__nv_bfloat16*)lat, (__nv_bfloat16*)kr);
+           page_size, rank, rot, S, first, (__nv_bfloat16*)lat, (__nv_bfloat16*)kr);
     BG_LAUNCH_CHECK();
     return BG_OK;
 }

@@ -39,6 +39,7 @@ struct LatentMmaParams {
     int H, hc;
     int rank, rot, rot_dims;
     int split, bq, stages;
+    int window;             // as first_visible() reads it; 0: every earlier position
     float scale;
     unsigned* status;
 };
@@ -81,7 +82,8 @@ latent_attention_mma_kernel(LatentMmaParams p) {
     float* l_s = m_s + ROWS;
     float* corr_s = l_s + ROWS;
     int* pos_s = reinterpret_cast<int*>(corr_s + ROWS);                                   // [ROWS] position, -1: no row
-    int* ok_s = pos_s + ROWS;                                                             // [stages][64] the key has a page
+    int* lo_s = pos_s + ROWS;                                                             // [ROWS] the first key the row sees
+    int* ok_s = lo_s + ROWS;                                                              // [stages][64] the key has a page
 
     pdl_launch();
     pdl_wait();
@@ -91,7 +93,9 @@ latent_attention_mma_kernel(LatentMmaParams p) {
     const int h0 = hchunk * p.hc;
     const int nh = min(p.hc, p.H - h0);
     const int pos_last = p.positions[row0 + nq - 1];
-    const int k_begin = sp * p.split;
+    const int lo_first = first_visible(p.positions[row0], p.window);
+    // the first tile that holds a key any row sees (tiles start at multiples of LM_TILE, as split does)
+    const int k_begin = max(sp * p.split, (lo_first / LM_TILE) * LM_TILE);
     const int k_end = min((sp + 1) * p.split, pos_last + 1);
     if (k_begin >= k_end) return;
 
@@ -128,6 +132,7 @@ latent_attention_mma_kernel(LatentMmaParams p) {
     for (int r = tid; r < ROWS; r += LM_THREADS) {
         m_s[r] = -INFINITY; l_s[r] = 0.0f; corr_s[r] = 1.0f;
         pos_s[r] = r < n_rows ? p.positions[row0 + r / nh] : -1;
+        lo_s[r] = r < n_rows ? first_visible(pos_s[r], p.window) : 0;
     }
 
     float acc[MT][NT][4];
@@ -211,7 +216,7 @@ latent_attention_mma_kernel(LatentMmaParams p) {
                     const int r = mt * 16 + g + (e >> 1) * 8;
                     const int j = warp * 8 + 2 * t4 + (e & 1);
                     const int key = t0 + j;
-                    const bool seen = key <= pos_s[r] && key < k_end && okt[j];
+                    const bool seen = key >= lo_s[r] && key <= pos_s[r] && key < k_end && okt[j];
                     s_s[r * LM_SS + j] = seen ? sc[mt][e] * p.scale : -INFINITY;
                 }
         }
@@ -281,7 +286,7 @@ latent_attention_mma_kernel(LatentMmaParams p) {
 #pragma unroll
         for (int hi = 0; hi < 2; ++hi) {
             const int r = mt * 16 + g + hi * 8;
-            if (r >= n_rows || pos_s[r] < k_begin) continue;
+            if (r >= n_rows || pos_s[r] < sp * p.split || lo_s[r] >= (sp + 1) * p.split) continue;
             const int qi = r / nh, hh = r - qi * nh;
             const size_t prow = ((size_t)(row0 + qi) * p.H + h0 + hh) * p.max_splits + sp;
 #pragma unroll
@@ -294,7 +299,7 @@ latent_attention_mma_kernel(LatentMmaParams p) {
             }
         }
     for (int r = tid; r < n_rows; r += LM_THREADS) {
-        if (pos_s[r] < k_begin) continue;
+        if (pos_s[r] < sp * p.split || lo_s[r] >= (sp + 1) * p.split) continue;
         const int qi = r / nh, hh = r - qi * nh;
         const size_t prow = ((size_t)(row0 + qi) * p.H + h0 + hh) * p.max_splits + sp;
         p.part_ml[prow * 2 + 0] = m_s[r];
@@ -309,7 +314,7 @@ using namespace bg;
 static size_t latent_mma_smem(int rows, int width, int stages) {
     const size_t ks = (size_t)width + 8;
     size_t b = (size_t)rows * ks * 2 + (size_t)stages * LM_TILE * ks * 2 + (size_t)rows * LM_PS * 2 + (size_t)rows * LM_SS * 4 +
-               (size_t)rows * 4 * 4 + (size_t)stages * LM_TILE * 4;
+               (size_t)rows * 5 * 4 + (size_t)stages * LM_TILE * 4;
     return (b + 15) / 16 * 16;
 }
 
@@ -331,7 +336,7 @@ extern "C" int bg_latent_attention_mma_partial(const float* q_lat, long long ql_
                                                int page_size, const int* block_table, int max_pages, const int* positions,
                                                const int* qblk, int n_qblk, float* part_o, float* part_ml, int max_splits,
                                                int n_splits_launch, int H, int hc, int rank, int rot, int rot_dims, int split,
-                                               int bq, int stages, float scale, unsigned* status, cudaStream_t stream) {
+                                               int bq, int stages, int window, float scale, unsigned* status, cudaStream_t stream) {
     if (n_qblk <= 0 || n_splits_launch <= 0) return BG_OK;
     const int width = rank + rot;
     if (H <= 0 || hc <= 0 || hc > H || width % 32 != 0 || rank % 8 != 0 || rank > 512 || rot_dims > rot || (rot_dims & 1))
@@ -346,7 +351,7 @@ extern "C" int bg_latent_attention_mma_partial(const float* q_lat, long long ql_
     p.qr_head = qr_head; p.qr_off = qr_off; p.cos_sin = cos_sin; p.pool = (const __nv_bfloat16*)pool; p.num_pages = num_pages;
     p.page_size = page_size; p.block_table = block_table; p.max_pages = max_pages; p.positions = positions; p.qblk = qblk;
     p.part_o = part_o; p.part_ml = part_ml; p.max_splits = max_splits; p.H = H; p.hc = hc; p.rank = rank; p.rot = rot;
-    p.rot_dims = rot_dims; p.split = split; p.bq = bq; p.stages = stages; p.scale = scale; p.status = status;
+    p.rot_dims = rot_dims; p.split = split; p.bq = bq; p.stages = stages; p.window = window; p.scale = scale; p.status = status;
     // stages: two CTAs on an SM overlap one another's loads, queries and epilogues, so a CTA takes no more than half
     // of an SM's shared memory where it can (with two tiles in flight if they fit that, else with one); a CTA too
     // large for that is alone on its SM and takes two tiles if they fit

@@ -21,7 +21,8 @@ template <typename TI, typename TW>
 __global__ void conv_silu_kernel(const TI* __restrict__ src, int src_stride, int col0, int channels, int taps,
                                  const TW* __restrict__ w, const TW* __restrict__ b, const float* __restrict__ state,
                                  size_t slot_stride, size_t conv_off, const int* __restrict__ slots,
-                                 const int* __restrict__ row_req, const int* __restrict__ reqs, float* __restrict__ out) {
+                                 const int* __restrict__ row_req, const int* __restrict__ reqs, float* __restrict__ out,
+                                 int act) {
     pdl_launch();
     pdl_wait();
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
@@ -39,7 +40,7 @@ __global__ void conv_silu_kernel(const TI* __restrict__ src, int src_stride, int
         else v = st[(size_t)(taps - 1 - (back - j)) * channels + c];
         acc = fmaf(to_float(w[(size_t)c * taps + k]), v, acc);
     }
-    out[(size_t)t * channels + c] = silu32(acc);
+    out[(size_t)t * channels + c] = act ? silu32(acc) : acc;
 }
 
 // The slot's conv state after the step: the last taps-1 inputs of (old state, the step's n rows).
@@ -315,7 +316,7 @@ using namespace bg;
 extern "C" int bg_conv_silu(const void* src, int src_dtype, int src_stride, int col0, int channels, int taps, const void* w,
                             const void* b, int w_dtype, float* state, long long slot_stride, long long conv_off,
                             const int* slots, const int* row_req, const int* reqs, int n_req, float* out, int n_rows,
-                            cudaStream_t stream) {
+                            int act, cudaStream_t stream) {
     if (n_rows <= 0 || n_req <= 0) return BG_OK;
     if (channels <= 0 || taps < 1 || n_req > 65535) return BG_ERR_SHAPE;
     const unsigned bx = (unsigned)((channels + 127) / 128);
@@ -323,7 +324,7 @@ extern "C" int bg_conv_silu(const void* src, int src_dtype, int src_stride, int 
     BG_DISPATCH_DTYPE(src_dtype, TI, BG_DISPATCH_DTYPE(w_dtype, TW,
         launch(conv_silu_kernel<TI, TW>, dim3(n_rows, bx), dim3(128), 0, stream, (const TI*)src, src_stride, col0, channels,
                taps, (const TW*)w, (const TW*)b, (const float*)state, (size_t)slot_stride, (size_t)conv_off, slots, row_req,
-               reqs, out)));
+               reqs, out, act)));
     BG_LAUNCH_CHECK();
     if (taps > 1) {
         BG_DISPATCH_DTYPE(src_dtype, TI,

@@ -20,16 +20,40 @@
 
 namespace bg {
 
-// One warp chooses for one token: `sc` holds the token's E logits in shared memory and is used up.  The choice is made on the
-// logits: sigmoid keeps their order, but rounds large ones to the same score.
-__device__ __forceinline__ void choose_experts(float* sc, int E, int top, int sigmoid, int renorm, int* __restrict__ ids,
+// How the router's logits become scores (`mode`): 0 the logit itself, 1 its sigmoid, 2 the softmax over all E logits.
+struct RouteRule {
+    int mode;
+    int renorm;             // the chosen scores are divided by their sum
+    const float* bias;      // [E] or null: added to the scores for the CHOICE only; the weights are the scores without it
+    float scale;            // multiplies the weights
+};
+
+// One warp chooses for one token: `sc` holds the token's E logits in shared memory and is used up.  Without a bias and
+// without the softmax the choice is made on the logits: sigmoid keeps their order, but rounds large ones to the same
+// score.  Otherwise it is made on score + bias, the scores formed anew from the logits each round; a logit of -inf marks
+// an expert that is taken.  Ties go to the lower index.
+__device__ __forceinline__ void choose_experts(float* sc, int E, int top, RouteRule rule, int* __restrict__ ids,
                                                float* __restrict__ weights, size_t t, int lane) {
     float total = 0.0f;
+    float zmax = 0.0f, inv = 1.0f;
+    if (rule.mode == 2) {                                  // softmax over all experts, float
+        float m = -INFINITY;
+        for (int e = lane; e < E; e += 32) m = fmaxf(m, sc[e]);
+        zmax = warp_max(m);
+        float s = 0.0f;
+        for (int e = lane; e < E; e += 32) s += expf(sc[e] - zmax);
+        inv = 1.0f / warp_sum(s);
+    }
+    const bool on_scores = rule.mode == 2 || rule.bias != nullptr;
+    auto score_of = [&](float z) {
+        return rule.mode == 2 ? expf(z - zmax) * inv : (rule.mode == 1 ? 1.0f / (1.0f + expf(-z)) : z);
+    };
     for (int j = 0; j < top; ++j) {
         float best = -INFINITY;
         int arg = 0x7fffffff;
         for (int e = lane; e < E; e += 32) {
-            const float v = sc[e];
+            float v = sc[e];
+            if (on_scores && v != -INFINITY) v = score_of(v) + (rule.bias ? rule.bias[e] : 0.0f);
             if (v > best) { best = v; arg = e; }            // ascending e: the first of equal scores stays
         }
 #pragma unroll
@@ -38,19 +62,21 @@ __device__ __forceinline__ void choose_experts(float* sc, int E, int top, int si
             const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
             if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
         }
-        const float score = sigmoid ? 1.0f / (1.0f + expf(-best)) : best;
+        if (arg == 0x7fffffff) arg = 0;                     // (every score NaN or -inf: a defined choice)
+        const float score = score_of(on_scores ? sc[arg] : best);
+        __syncwarp();
         if (lane == 0) {
             ids[(size_t)t * top + j] = arg;
-            weights[(size_t)t * top + j] = score;
+            weights[(size_t)t * top + j] = score * rule.scale;
             sc[arg] = -INFINITY;
         }
         total += score;
         __syncwarp();
     }
-    if (renorm && lane < top) weights[(size_t)t * top + lane] /= total;
+    if (rule.renorm && lane < top) weights[(size_t)t * top + lane] /= total;
 }
 
-__global__ void route_topk_kernel(const float* __restrict__ logits, int T, int E, int top, int sigmoid, int renorm,
+__global__ void route_topk_kernel(const float* __restrict__ logits, int T, int E, int top, RouteRule rule,
                                   int* __restrict__ ids, float* __restrict__ weights) {
     extern __shared__ float score_s[];                     // [warps][E]
     pdl_launch();
@@ -61,7 +87,7 @@ __global__ void route_topk_kernel(const float* __restrict__ logits, int T, int E
     float* sc = score_s + (size_t)warp * E;
     for (int e = lane; e < E; e += 32) sc[e] = logits[(size_t)t * E + e];
     __syncwarp();
-    choose_experts(sc, E, top, sigmoid, renorm, ids, weights, (size_t)t, lane);
+    choose_experts(sc, E, top, rule, ids, weights, (size_t)t, lane);
 }
 
 // The router of a step in one kernel: a block takes ROUTE_TOKENS tokens; each of its warps takes experts in turn and
@@ -71,7 +97,7 @@ __global__ void route_topk_kernel(const float* __restrict__ logits, int T, int E
 constexpr int ROUTE_TOKENS = 8, ROUTE_UNROLL = 8;
 template <typename TI>
 __global__ void __launch_bounds__(32 * ROUTE_TOKENS)
-route_kernel(const TI* __restrict__ h, int ldh, const float* __restrict__ W, int T, int d, int E, int top, int sigmoid, int renorm,
+route_kernel(const TI* __restrict__ h, int ldh, const float* __restrict__ W, int T, int d, int E, int top, RouteRule rule,
              int* __restrict__ ids, float* __restrict__ weights, float* __restrict__ logits_out) {
     extern __shared__ float logit_s[];                     // [ROUTE_TOKENS][E]
     pdl_launch();
@@ -111,7 +137,7 @@ route_kernel(const TI* __restrict__ h, int ldh, const float* __restrict__ W, int
         }
     }
     __syncthreads();
-    if (warp < n) choose_experts(logit_s + warp * E, E, top, sigmoid, renorm, ids, weights, (size_t)(t0 + warp), lane);
+    if (warp < n) choose_experts(logit_s + warp * E, E, top, rule, ids, weights, (size_t)(t0 + warp), lane);
 }
 
 // The same for a width that is a multiple of 8 and 16-byte aligned rows.  A block of eight warps takes TPB tokens, 8 / TPB
@@ -123,8 +149,8 @@ route_kernel(const TI* __restrict__ h, int ldh, const float* __restrict__ W, int
 // one at a time above cost 53 us for 1,536 features whatever the number of tokens.)
 template <typename TI, int TPB, int G>
 __global__ void __launch_bounds__(32 * ROUTE_TOKENS)
-route_vec8_kernel(const TI* __restrict__ h, int ldh, const float* __restrict__ W, int T, int d, int E, int top, int sigmoid,
-                  int renorm, int* __restrict__ ids, float* __restrict__ weights, float* __restrict__ logits_out) {
+route_vec8_kernel(const TI* __restrict__ h, int ldh, const float* __restrict__ W, int T, int d, int E, int top, RouteRule rule,
+                  int* __restrict__ ids, float* __restrict__ weights, float* __restrict__ logits_out) {
     constexpr int WPT = ROUTE_TOKENS / TPB;                // warps per token
     extern __shared__ float logit_s[];                     // [TPB][E]
     pdl_launch();
@@ -164,7 +190,7 @@ route_vec8_kernel(const TI* __restrict__ h, int ldh, const float* __restrict__ W
         }
     }
     __syncthreads();                                       // every warp comes here, with or without a token
-    if (live && wq == 0) choose_experts(sc, E, top, sigmoid, renorm, ids, weights, (size_t)t, lane);
+    if (live && wq == 0) choose_experts(sc, E, top, rule, ids, weights, (size_t)t, lane);
 }
 
 __global__ void __launch_bounds__(1024)
@@ -224,6 +250,49 @@ __global__ void route_combine_kernel(const TY* __restrict__ yp, const float* __r
         }
         out[(size_t)t * d + i] = acc;
     }
+}
+
+// The same sum for a layer that also has experts without weights and a shared expert:
+//   out[t] = sum_j w_j (id_j < n_real ? yp[row_of[t top + j]] : h[t])  +  sigmoid(sg[t]) shared[t].
+// An expert whose index is n_real or more returns its input (the step's rows h in the compute type).  `shared` [T][d]
+// float is the result of an expert that every token passes, `sg` one number per token (element t at sg[t * sg_stride]),
+// whose sigmoid multiplies it; without `sg` the shared result is added as it is.  Ranks in index order, float.
+template <typename TY, typename TH>
+__global__ void route_combine_ext_kernel(const TY* __restrict__ yp, const float* __restrict__ weights, const int* __restrict__ row_of,
+                                         const int* __restrict__ ids, int n_real, const TH* __restrict__ h, int ldh,
+                                         const float* __restrict__ shared, const float* __restrict__ sg, int sg_stride,
+                                         float* __restrict__ out, int T, int d, int top) {
+    pdl_launch();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const float sgate = shared ? (sg ? 1.0f / (1.0f + expf(-sg[(size_t)t * sg_stride])) : 1.0f) : 0.0f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        float acc = 0.0f;
+        for (int j = 0; j < top; ++j) {
+            const int a = t * top + j;
+            const float v = ids[a] < n_real ? to_float(yp[(size_t)row_of[a] * d + i]) : to_float(h[(size_t)t * ldh + i]);
+            acc = fmaf(weights[a], v, acc);
+        }
+        if (shared) acc = fmaf(sgate, shared[(size_t)t * d + i], acc);
+        out[(size_t)t * d + i] = acc;
+    }
+}
+
+// A gated expert's activation with clamps: from a row [gate (n) | up (n)] of the product,
+//   g = min(gate, limit), u = clamp(up, -limit, limit), out = g sigmoid(alpha g) (u + 1).
+// Float arithmetic; the input in either type with `ld` elements between rows, the output contiguous.
+template <typename TI, typename TO>
+__global__ void glu_clamped_kernel(const TI* __restrict__ gu, int ld, TO* __restrict__ out, size_t total, int n, float limit,
+                                   float alpha) {
+    pdl_launch();
+    pdl_wait();
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const size_t r = idx / n;
+    const int i = (int)(idx - r * n);
+    const float g = fminf(to_float(gu[r * ld + i]), limit);
+    const float u = fminf(fmaxf(to_float(gu[r * ld + n + i]), -limit), limit);
+    out[idx] = from_float<TO>(g / (1.0f + expf(-alpha * g)) * (u + 1.0f));
 }
 
 // ------------------------------------------------------------------------------------------------ grouped product
@@ -369,36 +438,38 @@ extern "C" int bg_route_logits(const void* A, int a_dtype, int lda, const float*
     return BG_OK;
 }
 
-extern "C" int bg_route_topk(const float* logits, int T, int E, int top, int sigmoid, int renorm, int* ids, float* weights,
-                             cudaStream_t stream) {
+extern "C" int bg_route_topk(const float* logits, int T, int E, int top, int mode, int renorm, const float* bias, float scale,
+                             int* ids, float* weights, cudaStream_t stream) {
     if (T <= 0) return BG_OK;
-    if (E <= 0 || top <= 0 || top > E || top > 32) return BG_ERR_SHAPE;
+    if (E <= 0 || top <= 0 || top > E || top > 32 || mode < 0 || mode > 2) return BG_ERR_SHAPE;
+    const RouteRule rule = {mode, renorm, bias, scale};
     const int warps = 4;
     const size_t smem = (size_t)warps * E * sizeof(float);
     if (smem > 40 * 1024) return BG_ERR_UNSUPPORTED;
-    launch(route_topk_kernel, dim3((T + warps - 1) / warps), dim3(32 * warps), smem, stream, logits, T, E, top, sigmoid, renorm, ids,
+    launch(route_topk_kernel, dim3((T + warps - 1) / warps), dim3(32 * warps), smem, stream, logits, T, E, top, rule, ids,
            weights);
     BG_LAUNCH_CHECK();
     return BG_OK;
 }
 
 // The router in one kernel: float logits of h [T, d] (either type, row stride ldh) against W [E, d] float, and the choice.
-extern "C" int bg_route(const void* h, int h_dtype, int ldh, const float* W, int T, int d, int E, int top, int sigmoid, int renorm,
-                        int* ids, float* weights, float* logits_out, cudaStream_t stream) {
+extern "C" int bg_route(const void* h, int h_dtype, int ldh, const float* W, int T, int d, int E, int top, int mode, int renorm,
+                        const float* bias, float scale, int* ids, float* weights, float* logits_out, cudaStream_t stream) {
     if (T <= 0) return BG_OK;
-    if (E <= 0 || top <= 0 || top > E || top > 32 || d <= 0) return BG_ERR_SHAPE;
+    if (E <= 0 || top <= 0 || top > E || top > 32 || d <= 0 || mode < 0 || mode > 2) return BG_ERR_SHAPE;
+    const RouteRule rule = {mode, renorm, bias, scale};
     const size_t smem = (size_t)ROUTE_TOKENS * E * sizeof(float);
     if (smem > 40 * 1024) return BG_ERR_UNSUPPORTED;
     const dim3 grid((T + ROUTE_TOKENS - 1) / ROUTE_TOKENS), block(32 * ROUTE_TOKENS);
     if (d % 8 == 0 && ldh % 8 == 0 && (uintptr_t)h % 16 == 0 && (uintptr_t)W % 16 == 0 && T <= 256)
         BG_DISPATCH_DTYPE(h_dtype, TI, launch(route_vec8_kernel<TI, 1, 1>, dim3(T), block, (size_t)E * sizeof(float), stream,
-                                              (const TI*)h, ldh, W, T, d, E, top, sigmoid, renorm, ids, weights, logits_out));
+                                              (const TI*)h, ldh, W, T, d, E, top, rule, ids, weights, logits_out));
     else if (d % 8 == 0 && ldh % 8 == 0 && (uintptr_t)h % 16 == 0 && (uintptr_t)W % 16 == 0)
         BG_DISPATCH_DTYPE(h_dtype, TI, launch(route_vec8_kernel<TI, ROUTE_TOKENS, 4>, grid, block, smem, stream, (const TI*)h, ldh, W,
-                                              T, d, E, top, sigmoid, renorm, ids, weights, logits_out));
+                                              T, d, E, top, rule, ids, weights, logits_out));
     else
-        BG_DISPATCH_DTYPE(h_dtype, TI, launch(route_kernel<TI>, grid, block, smem, stream, (const TI*)h, ldh, W, T, d, E, top, sigmoid,
-                                              renorm, ids, weights, logits_out));
+        BG_DISPATCH_DTYPE(h_dtype, TI, launch(route_kernel<TI>, grid, block, smem, stream, (const TI*)h, ldh, W, T, d, E, top, rule,
+                                              ids, weights, logits_out));
     BG_LAUNCH_CHECK();
     return BG_OK;
 }
@@ -428,6 +499,32 @@ extern "C" int bg_route_combine(const void* yp, int y_dtype, const float* weight
     const int threads = d >= 256 ? 256 : ((d + 31) / 32) * 32;
     BG_DISPATCH_DTYPE(y_dtype, TY, launch(route_combine_kernel<TY>, dim3(T), dim3(threads), 0, stream, (const TY*)yp, weights, row_of,
                                           out, T, d, top, scale));
+    BG_LAUNCH_CHECK();
+    return BG_OK;
+}
+
+extern "C" int bg_route_combine_ext(const void* yp, int y_dtype, const float* weights, const int* row_of, const int* ids, int n_real,
+                                    const void* h, int h_dtype, int ldh, const float* shared, const float* sg, int sg_stride,
+                                    float* out, int T, int d, int top, cudaStream_t stream) {
+    if (T <= 0) return BG_OK;
+    if (!ids || !h || top <= 0) return BG_ERR_SHAPE;
+    const int threads = d >= 256 ? 256 : ((d + 31) / 32) * 32;
+    BG_DISPATCH_DTYPE(y_dtype, TY, BG_DISPATCH_DTYPE(h_dtype, TH,
+        launch(route_combine_ext_kernel<TY, TH>, dim3(T), dim3(threads), 0, stream, (const TY*)yp, weights, row_of, ids, n_real,
+               (const TH*)h, ldh, shared, sg, sg_stride, out, T, d, top)));
+    BG_LAUNCH_CHECK();
+    return BG_OK;
+}
+
+extern "C" int bg_glu_clamped(const void* gu, int gu_dtype, int ld, void* out, int out_dtype, int rows, int n, float limit,
+                              float alpha, cudaStream_t stream) {
+    if (rows <= 0 || n <= 0) return BG_OK;
+    if (ld < 2 * n) return BG_ERR_SHAPE;
+    const size_t total = (size_t)rows * n;
+    if ((total + 255) / 256 > 0x7fffffffULL) return BG_ERR_SHAPE;
+    BG_DISPATCH_DTYPE(gu_dtype, TI, BG_DISPATCH_DTYPE(out_dtype, TO,
+        launch(glu_clamped_kernel<TI, TO>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, (const TI*)gu, ld, (TO*)out,
+               total, n, limit, alpha)));
     BG_LAUNCH_CHECK();
     return BG_OK;
 }

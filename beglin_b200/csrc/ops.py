@@ -48,9 +48,21 @@ _SIGNATURES = {
                                _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p,
                                _c_void_p],
     "bg_route_logits": [_c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
-    "bg_route_topk": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p],
-    "bg_route": [_c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p,
-                 _c_void_p, _c_void_p],
+    "bg_route_topk": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_float, _c_void_p, _c_void_p, _c_void_p],
+    "bg_route": [_c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_float,
+                 _c_void_p, _c_void_p, _c_void_p, _c_void_p],
+    "bg_route_combine_ext": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p,
+                             _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
+    "bg_glu_clamped": [_c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_float, _c_float, _c_void_p],
+    "bg_lane_step": [_c_void_p, _c_int, _c_ll, _c_void_p, _c_int, _c_int, _c_ll, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+                     _c_float, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p],
+    "bg_lane_fill": [_c_void_p, _c_void_p, _c_ll, _c_int, _c_void_p],
+    "bg_rglru_scan": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_ll,
+                      _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+    "bg_rglru_scan_chunked": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_ll,
+                              _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_int,
+                              _c_int, _c_int, _c_void_p],
+    "bg_rglru_softplus": [_c_void_p, _c_int, _c_float, _c_void_p, _c_int, _c_void_p],
     "bg_route_sort": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
     "bg_route_gather": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "bg_route_combine": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
@@ -108,20 +120,20 @@ _SIGNATURES = {
     "bg_latent_attention_partial": [_c_void_p, _c_int, _c_ll, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p,
                                     _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int,
                                     _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
-                                    _c_int, _c_int, _c_float, _c_void_p, _c_void_p],
+                                    _c_int, _c_int, _c_int, _c_float, _c_void_p, _c_void_p],
     "bg_latent_attention_merge": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int,
-                                  _c_int, _c_int, _c_void_p],
+                                  _c_int, _c_int, _c_int, _c_void_p],
     "bg_latent_attention_mma_plan": [_c_int, _c_int, ctypes.POINTER(_c_int), ctypes.POINTER(_c_int)],
     "bg_latent_attention_mma_partial": [_c_void_p, _c_ll, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_int,
                                         _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int,
-                                        _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
+                                        _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
                                         _c_void_p, _c_void_p],
-    "bg_latent_gather": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p,
+    "bg_latent_gather": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p,
                          _c_void_p],
     "bg_latent_expand": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
     "bg_rotate_q": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_void_p],
     "bg_conv_silu": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_ll, _c_ll,
-                     _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p],
+                     _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p],
     "bg_ssm_scan": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p,
                     _c_ll, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "bg_gated_group_rmsnorm": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_float, _c_void_p, _c_int,
@@ -1076,13 +1088,14 @@ def latent_attention(q_lat: torch.Tensor, q_raw: torch.Tensor, dim: int, rot: in
                      cos_sin: Optional[torch.Tensor], pool: torch.Tensor, block_table: torch.Tensor,
                      positions: torch.Tensor, qblk: torch.Tensor, n_qblk: int, max_position: int, bq: int, hc: int,
                      tile: int, split: int, scale: float, out: torch.Tensor, status: Optional[torch.Tensor],
-                     mma_stages: int = 0) -> None:
+                     mma_stages: int = 0, window: int = 0) -> None:
     """Causal attention of a step's rows over the latent cache.  q_lat float32 [H, T, rank]: the queries carried into
     the latent space; q_raw [T, H * (dim + rot)]: the query product's rows, whose rot part is rotated here; pool
     [pages, page_size, rank + rot]; out [H, T, rank] receives, per head, the softmax-weighted sum of the cached
     latents.  `qblk` is cut for `bq` rows; a CTA takes `hc` heads; keys are cut into splits of `split` positions.
     With `mma_stages` 1 or 2 the products run on the tensor cores (bfloat16 q_raw and pool, bq * hc at most 64, sizes as
-    `latent_attention_mma_plan` says); else on the CUDA cores in float, for every size and type."""
+    `latent_attention_mma_plan` says); else on the CUDA cores in float, for every size and type.  `window` w > 0: a row
+    sees itself and the w - 1 positions before it."""
     _cuda(q_lat, q_raw, cos_sin, pool, block_table, positions, qblk, out, status)
     _i32(positions, "positions"); _i32(block_table, "block_table"); _i32(qblk, "qblk")
     H, T, rank = q_lat.shape
@@ -1107,31 +1120,32 @@ def latent_attention(q_lat: torch.Tensor, q_raw: torch.Tensor, dim: int, rot: in
                                                      dim + rot, dim, _p(cos_sin), _p(pool), pool.shape[0], pool.shape[1],
                                                      _p(block_table), block_table.shape[1], _p(positions), _p(qblk), n_qblk,
                                                      _p(part_o), _p(part_ml), n_splits, n_splits, H, hc, rank, rot, rot_dims,
-                                                     split, bq, mma_stages, float(scale), _p(status), _stream()),
+                                                     split, bq, mma_stages, int(window), float(scale), _p(status), _stream()),
                    "latent_attention_mma_partial")
         else:
             _check(L.bg_latent_attention_partial(_p(q_lat), _dt(q_lat), q_lat.stride(0), q_lat.stride(1), _p(q_raw), _dt(q_raw),
                                                  q_raw.stride(0), dim + rot, dim, _p(cos_sin), _p(pool), _dt(pool), pool.shape[0],
                                                  pool.shape[1], _p(block_table), block_table.shape[1], _p(positions), _p(qblk),
                                                  n_qblk, _p(part_o), _p(part_ml), n_splits, n_splits, H, hc, rank, rot, rot_dims,
-                                                 split, tile, bq, float(scale), _p(status), _stream()), "latent_attention_partial")
+                                                 split, tile, bq, int(window), float(scale), _p(status), _stream()), "latent_attention_partial")
         _check(L.bg_latent_attention_merge(_p(part_o), _p(part_ml), _p(positions), _p(out), _dt(out), out.stride(0),
-                                           out.stride(1), T, H, rank, n_splits, split, _stream()), "latent_attention_merge")
+                                           out.stride(1), T, H, rank, n_splits, split, int(window), _stream()), "latent_attention_merge")
 
 
-def latent_gather(pool: torch.Tensor, block_table: torch.Tensor, req: int, rank: int, lat: torch.Tensor, kr: torch.Tensor) -> None:
-    """lat[s] and kr[s] = the latent and the rotated key part of the cached row of position s < S of the step's request
-    `req` (zeros where it holds no page); pool [pages, page_size, rank + rot], lat [S, rank], kr [S, rot], bfloat16."""
+def latent_gather(pool: torch.Tensor, block_table: torch.Tensor, req: int, rank: int, lat: torch.Tensor, kr: torch.Tensor,
+                  first: int = 0) -> None:
+    """lat[s] and kr[s] = the latent and the rotated key part of the cached row of position first + s, s < S, of the step's
+    request `req` (zeros where it holds no page); pool [pages, page_size, rank + rot], lat [S, rank], kr [S, rot], bfloat16."""
     _cuda(pool, block_table, lat, kr)
     _i32(block_table, "block_table")
     S, rot = lat.shape[0], pool.shape[2] - rank
     if pool.dtype != torch.bfloat16 or lat.dtype != torch.bfloat16 or kr.dtype != torch.bfloat16 or pool.dim() != 3 \
             or not pool.is_contiguous() or tuple(lat.shape) != (S, rank) or tuple(kr.shape) != (S, rot) \
-            or not lat.is_contiguous() or not kr.is_contiguous() or not 0 <= req < block_table.shape[0]:
+            or not lat.is_contiguous() or (rot and not kr.is_contiguous()) or not 0 <= req < block_table.shape[0] or first < 0:
         raise KernelError("latent_gather: a bfloat16 pool [pages, page, rank + rot], lat [S, rank] and kr [S, rot]")
     with phase("kv_expand"):
         _check(lib().bg_latent_gather(_p(pool), _p(block_table), block_table.shape[1], req, pool.shape[0], pool.shape[1],
-                                      rank, rot, S, _p(lat), _p(kr), _stream()), "latent_gather")
+                                      rank, rot, S, int(first), _p(lat), _p(kr), _stream()), "latent_gather")
 
 
 def latent_expand(kv: torch.Tensor, kr: torch.Tensor, H: int, dim: int, pages: torch.Tensor) -> None:
@@ -1144,7 +1158,7 @@ def latent_expand(kv: torch.Tensor, kr: torch.Tensor, H: int, dim: int, pages: t
     for t in (kv, kr, pages):
         if t.dtype != torch.bfloat16:
             raise KernelError("latent_expand takes bfloat16 tensors")
-    if kv.stride(1) != 1 or kv.shape[1] != H * dim + H * hd or kr.shape[0] != S or not kr.is_contiguous() or dim % 8 or rot % 8 \
+    if kv.stride(1) != 1 or kv.shape[1] != H * dim + H * hd or kr.shape[0] != S or (rot and not kr.is_contiguous()) or dim % 8 or rot % 8 \
             or kv.stride(0) % 8 or kv.data_ptr() % 16:
         raise KernelError(f"latent_expand: kv is {tuple(kv.shape)}, kr {tuple(kr.shape)}")
     if tuple(pages.shape) != (-(-S // 64), 2, H, 64, hd) or not pages.is_contiguous():
@@ -1170,9 +1184,9 @@ def rotate_q(q: torch.Tensor, H: int, head: int, off: int, rot_dims: int, cos_si
 # The Mamba-2 recurrence
 def conv_silu(src: torch.Tensor, col0: int, channels: int, weight: torch.Tensor, bias: torch.Tensor, state: torch.Tensor,
               conv_off: int, slots: torch.Tensor, row_req: torch.Tensor, reqs: torch.Tensor, n_req: int,
-              out: torch.Tensor) -> None:
-    """The causal convolution per channel with SiLU over src[:, col0 : col0 + channels], continued from and into the
-    slots' conv state.  weight [channels, taps] (last column the current token's), bias [channels]; state float32
+              out: torch.Tensor, activation: str = "silu") -> None:
+    """The causal convolution per channel with SiLU (`activation` "none": without it) over src[:, col0 : col0 + channels],
+    continued from and into the slots' conv state.  weight [channels, taps] (last column the current token's), bias [channels]; state float32
     [slots, slot size] with the conv state, (taps - 1) x channels, at conv_off; reqs int32 [n_req, 3] = (request,
     first row, rows); out float32 [T, channels]."""
     _cuda(src, weight, bias, state, slots, row_req, reqs, out)
@@ -1188,10 +1202,12 @@ def conv_silu(src: torch.Tensor, col0: int, channels: int, weight: torch.Tensor,
         raise KernelError(f"conv_silu: the state is {tuple(state.shape)}")
     if out.dtype != torch.float32 or tuple(out.shape) != (T, channels) or not out.is_contiguous():
         raise KernelError("conv_silu: out is float32 [T, channels]")
+    if activation not in ("silu", "none"):
+        raise KernelError(f"conv_silu: unknown activation '{activation}' (silu, none)")
     with phase("conv"):
         _check(lib().bg_conv_silu(_p(src), _dt(src), src.stride(0), col0, channels, taps, _p(weight), _p(bias), _dt(weight),
                                   _p(state), state.stride(0), conv_off, _p(slots), _p(row_req), _p(reqs), n_req, _p(out), T,
-                                  _stream()), "conv_silu")
+                                  1 if activation == "silu" else 0, _stream()), "conv_silu")
     if taps > 1:
         count_launches(1)
 
@@ -1440,10 +1456,22 @@ def route_logits(h: torch.Tensor, router: torch.Tensor, out: torch.Tensor) -> No
         _check(lib().bg_route_logits(_p(h), _dt(h), h.stride(0), _p(router), d, _p(out), E, T, E, d, _stream()), "route_logits")
 
 
-def route_topk(logits: torch.Tensor, top: int, ids: torch.Tensor, weights: torch.Tensor, sigmoid: bool = True,
-               renorm: bool = False) -> None:
+ROUTER_MODES = {"none": 0, "sigmoid": 1, "softmax": 2}
+
+
+def _route_rule(E: int, sigmoid, bias: Optional[torch.Tensor], what: str) -> int:
+    """The kernels' score mode from `sigmoid` (True, False, or one of ROUTER_MODES), with the choice bias checked."""
+    mode = ROUTER_MODES[sigmoid] if isinstance(sigmoid, str) else (1 if sigmoid else 0)
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != E or not bias.is_contiguous()):
+        raise KernelError(f"{what}: the choice bias is contiguous float32, one number per expert")
+    return mode
+
+
+def route_topk(logits: torch.Tensor, top: int, ids: torch.Tensor, weights: torch.Tensor, sigmoid=True,
+               renorm: bool = False, bias: Optional[torch.Tensor] = None, scale: float = 1.0) -> None:
     """Per row of float logits [T, E]: the `top` experts of largest score into ids [T, top] (int32) and their scores
-    into weights [T, top] (float32)."""
+    into weights [T, top] (float32).  `sigmoid` may name the score: "none", "sigmoid" or "softmax" (over all E).  `bias`
+    [E] is added to the scores for the choice only; `scale` multiplies the weights."""
     _cuda(logits, ids, weights)
     T, E = logits.shape
     _i32(ids, "ids")
@@ -1451,15 +1479,16 @@ def route_topk(logits: torch.Tensor, top: int, ids: torch.Tensor, weights: torch
             or tuple(ids.shape) != (T, top) or tuple(weights.shape) != (T, top) or not ids.is_contiguous() or not weights.is_contiguous():
         raise KernelError("route_topk: logits float32 [T, E], ids int32 [T, top], weights float32 [T, top]")
     with phase("router"):
-        _check(lib().bg_route_topk(_p(logits), T, E, top, 1 if sigmoid else 0, 1 if renorm else 0, _p(ids), _p(weights), _stream()),
-               "route_topk")
+        _check(lib().bg_route_topk(_p(logits), T, E, top, _route_rule(E, sigmoid, bias, "route_topk"), 1 if renorm else 0, _p(bias),
+                                   float(scale), _p(ids), _p(weights), _stream()), "route_topk")
 
 
-def route(h: torch.Tensor, router: torch.Tensor, top: int, ids: torch.Tensor, weights: torch.Tensor, sigmoid: bool = True,
-          renorm: bool = False, logits: Optional[torch.Tensor] = None) -> None:
+def route(h: torch.Tensor, router: torch.Tensor, top: int, ids: torch.Tensor, weights: torch.Tensor, sigmoid=True,
+          renorm: bool = False, logits: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
+          scale: float = 1.0) -> None:
     """`route_logits` and `route_topk` as one kernel: h [T, d] in either type, router float32 [E, d], ids int32 [T, top],
     weights float32 [T, top]; `logits`, when given, receives the float logits [T, E]."""
-    _cuda(h, router, ids, weights, logits)
+    _cuda(h, router, ids, weights, logits, bias)
     T, d = h.shape
     E = router.shape[0]
     _i32(ids, "ids")
@@ -1470,8 +1499,8 @@ def route(h: torch.Tensor, router: torch.Tensor, top: int, ids: torch.Tensor, we
     if logits is not None and (logits.dtype != torch.float32 or tuple(logits.shape) != (T, E) or not logits.is_contiguous()):
         raise KernelError("route: logits float32 [T, E]")
     with phase("router"):
-        _check(lib().bg_route(_p(h), _dt(h), h.stride(0), _p(router), T, d, E, top, 1 if sigmoid else 0, 1 if renorm else 0, _p(ids),
-                              _p(weights), _p(logits), _stream()), "route")
+        _check(lib().bg_route(_p(h), _dt(h), h.stride(0), _p(router), T, d, E, top, _route_rule(E, sigmoid, bias, "route"),
+                              1 if renorm else 0, _p(bias), float(scale), _p(ids), _p(weights), _p(logits), _stream()), "route")
 
 
 def route_sort(ids: torch.Tensor, E: int, offsets: torch.Tensor, row_of: torch.Tensor, src_of: torch.Tensor) -> None:
@@ -1506,6 +1535,142 @@ def route_combine(yp: torch.Tensor, weights: torch.Tensor, row_of: torch.Tensor,
     with phase("router"):
         _check(lib().bg_route_combine(_p(yp), _dt(yp), _p(weights), _p(row_of), _p(out), T, d, top, 1 if scale else 0, _stream()),
                "route_combine")
+
+
+def route_combine_ext(yp: torch.Tensor, weights: torch.Tensor, row_of: torch.Tensor, ids: torch.Tensor, n_real: int, h: torch.Tensor,
+                      out: torch.Tensor, top: int, shared: Optional[torch.Tensor] = None, sg: Optional[torch.Tensor] = None) -> None:
+    """out[t] = sum over j < top of weights[t top + j] * (yp[row_of[t top + j]] if ids[t top + j] < n_real else h[t])
+    + sigmoid(sg[t]) * shared[t]: experts from n_real on return their input h [T, d] (either type, unit inner stride).
+    `shared` float32 [T, d] contiguous and `sg` float32 [T] (any stride) may be absent; without sg the shared rows are added
+    as they are."""
+    _cuda(yp, weights, row_of, ids, h, out, shared, sg)
+    _i32(row_of, "row_of"); _i32(ids, "ids")
+    T, d = out.shape
+    if out.dtype != torch.float32 or not yp.is_contiguous() or not out.is_contiguous() or tuple(yp.shape) != (T * top, d) \
+            or tuple(h.shape) != (T, d) or h.stride(1) != 1 or ids.numel() != T * top or weights.numel() != T * top \
+            or weights.dtype != torch.float32:
+        raise KernelError("route_combine_ext: yp [T * top, d], h [T, d], out float32 [T, d], ids and weights [T * top]")
+    if shared is not None and (shared.dtype != torch.float32 or tuple(shared.shape) != (T, d) or not shared.is_contiguous()):
+        raise KernelError("route_combine_ext: shared float32 [T, d]")
+    if sg is not None and (shared is None or sg.dtype != torch.float32 or sg.dim() != 1 or sg.numel() != T):
+        raise KernelError("route_combine_ext: sg float32 [T] beside shared rows")
+    with phase("router"):
+        _check(lib().bg_route_combine_ext(_p(yp), _dt(yp), _p(weights), _p(row_of), _p(ids), int(n_real), _p(h), _dt(h), h.stride(0),
+                                          _p(shared), _p(sg), sg.stride(0) if sg is not None else 0, _p(out), T, d, top,
+                                          _stream()), "route_combine_ext")
+
+
+def glu_clamped(gate_up: torch.Tensor, out: torch.Tensor, limit: float, alpha: float = 1.702) -> None:
+    """out[r, i] = g sigmoid(alpha g) (u + 1) with g = min(gate_up[r, i], limit), u = clamp(gate_up[r, n + i], -limit, limit),
+    n = out.shape[1]: gate_up [rows, >= 2 n] of either type with unit inner stride, out contiguous [rows, n]."""
+    _cuda(gate_up, out)
+    rows, n = out.shape
+    if gate_up.dim() != 2 or gate_up.shape[0] != rows or gate_up.shape[1] < 2 * n or gate_up.stride(1) != 1 or not out.is_contiguous() \
+            or not limit > 0.0:
+        raise KernelError("glu_clamped: gate_up [rows, >= 2 n], out contiguous [rows, n], a positive limit")
+    with phase("swiglu"):
+        _check(lib().bg_glu_clamped(_p(gate_up), _dt(gate_up), gate_up.stride(0), _p(out), _dt(out), rows, n, float(limit),
+                                    float(alpha), _stream()), "glu_clamped")
+
+
+# ---------------------------------------------------------------------------------------------------- a residual in lanes
+def lane_fill(x: torch.Tensor, lanes: torch.Tensor) -> None:
+    """lanes[a] = x for every lane a: x float32 [T, d], lanes float32 [n, T, d], both contiguous."""
+    _cuda(x, lanes)
+    if x.dtype != torch.float32 or lanes.dtype != torch.float32 or not x.is_contiguous() or not lanes.is_contiguous() \
+            or tuple(lanes.shape[1:]) != tuple(x.shape):
+        raise KernelError("lane_fill: x float32 [T, d], lanes float32 [n, T, d]")
+    with phase("residuals"):
+        _check(lib().bg_lane_fill(_p(x), _p(lanes), x.numel(), lanes.shape[0], _stream()), "lane_fill")
+
+
+def lane_step(lanes: torch.Tensor, owed: Optional[torch.Tensor] = None, mix: Optional[torch.Tensor] = None,
+              out_weights: Optional[torch.Tensor] = None, in_weights: Optional[torch.Tensor] = None,
+              norm_weight: Optional[torch.Tensor] = None, eps: float = 0.0, h: Optional[torch.Tensor] = None,
+              z: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None) -> None:
+    """One pass over a residual kept in lanes, float32 [n, T, d].  With `owed` (a sublayer's result [T, d] in either type, or
+    float partial sums [parts, T, d]) the lanes are first rewritten, all at once: lane b <- sum_a mix[a, b] lane a +
+    out_weights[b] owed.  Then the read sum_a in_weights[a] lane a (ones when absent) goes to `z` (float32) as it is and/or
+    to `h` RMS-normed with `norm_weight` (float32 [d]) and `eps`.  With `rows` (int32) only those rows are read, and
+    nothing is written back."""
+    _cuda(lanes, owed, mix, out_weights, in_weights, norm_weight, h, z, rows)
+    if lanes.dtype != torch.float32 or lanes.dim() != 3 or not lanes.is_contiguous():
+        raise KernelError("lane_step: the lanes are contiguous float32 [n, T, d]")
+    n, T, d = lanes.shape
+    for name, t, count in (("mix", mix, n * n), ("out_weights", out_weights, n), ("in_weights", in_weights, n), ("norm_weight", norm_weight, d)):
+        if t is not None and (t.dtype != torch.float32 or t.numel() != count or not t.is_contiguous()):
+            raise KernelError(f"lane_step: {name} is contiguous float32 with {count} values")
+    parts, stride = 0, 0
+    if owed is not None:
+        parts, stride = _parts(owed, "lane_step: owed")
+        if tuple(owed.shape[-2:]) != (T, d) or not owed.is_contiguous() or mix is None or out_weights is None:
+            raise KernelError("lane_step: the owed result is contiguous [T, d] (or [parts, T, d]) and comes with mix and out_weights")
+    n_rows = T
+    if rows is not None:
+        _i32(rows, "rows")
+        n_rows = rows.numel()
+    for name, t in (("h", h), ("z", z)):
+        if t is not None and (tuple(t.shape) != (n_rows, d) or not t.is_contiguous()):
+            raise KernelError(f"lane_step: {name} is contiguous [{n_rows}, {d}]")
+    if z is not None and z.dtype != torch.float32:
+        raise KernelError("lane_step: z is float32")
+    if h is not None and norm_weight is None:
+        raise KernelError("lane_step: the normed read wants a norm weight")
+    with phase("rmsnorm"):
+        _check(lib().bg_lane_step(_p(lanes), n, T * d, _p(owed), _dt(owed) if owed is not None else F32, parts, stride, _p(mix),
+                                  _p(out_weights), _p(in_weights), _p(norm_weight), float(eps), _p(h),
+                                  _dt(h) if h is not None else F32, _p(z), _p(rows), n_rows, d, _stream()), "lane_step")
+
+
+# ---------------------------------------------------------------------------------------------------- gated linear recurrence
+def rglru_softplus(lam: torch.Tensor, scale: float, out: torch.Tensor) -> None:
+    """out[c] = scale * softplus(lam[c]), float32."""
+    _cuda(lam, out)
+    if out.dtype != torch.float32 or out.numel() != lam.numel() or not lam.is_contiguous() or not out.is_contiguous():
+        raise KernelError("rglru_softplus: out float32 of lam's size")
+    _check(lib().bg_rglru_softplus(_p(lam), _dt(lam), float(scale), _p(out), lam.numel(), _stream()), "rglru_softplus")
+
+
+def rglru_scan(gates: torch.Tensor, u: torch.Tensor, src: torch.Tensor, y_col: int, gate_bias_r: torch.Tensor,
+               gate_bias_i: torch.Tensor, decay: torch.Tensor, state: torch.Tensor, slots: torch.Tensor, reqs: torch.Tensor,
+               n_req: int, out: torch.Tensor, chunked: Optional[tuple] = None) -> None:
+    """The gated linear recurrence of a step.  gates float32 [blocks, T, 2 bs] (per block the recurrence gate's and the
+    input gate's products), u float32 [T, W] the convolved input, src float32 rows whose columns y_col .. y_col + W are
+    the other branch, the gates' biases and `decay` (= C softplus(lam)) float32 [W], state float32 [slots, size] with
+    the W states first, reqs int32 [n_req, 3] = (request, first row, rows), out [T, W] in either type.  `chunked` =
+    (chunks, n_chunks, longs, n_long, chunk_rows) instead of reqs: those requests' rows in chunks (`cut_long_requests`)."""
+    _cuda(gates, u, src, gate_bias_r, gate_bias_i, decay, state, slots, reqs, out)
+    _i32(slots, "slots")
+    T, W = u.shape
+    blocks = gates.shape[0]
+    for t in (gates, u, gate_bias_r, gate_bias_i, decay):
+        if t.dtype != torch.float32 or not t.is_contiguous():
+            raise KernelError("rglru_scan: gates, u, biases and decay are contiguous float32")
+    if W % blocks or tuple(gates.shape) != (blocks, T, 2 * (W // blocks)) or gate_bias_r.numel() != W or gate_bias_i.numel() != W \
+            or decay.numel() != W:
+        raise KernelError(f"rglru_scan: gates {tuple(gates.shape)} do not fit u {tuple(u.shape)}")
+    if src.dtype != torch.float32 or src.dim() != 2 or src.stride(1) != 1 or src.shape[0] < T or y_col + W > src.shape[1]:
+        raise KernelError("rglru_scan: src float32 rows with the other branch's W columns from y_col")
+    if state.dtype != torch.float32 or state.dim() != 2 or state.stride(1) != 1 or state.shape[1] < W:
+        raise KernelError(f"rglru_scan: the state is {tuple(state.shape)}")
+    if tuple(out.shape) != (T, W) or not out.is_contiguous():
+        raise KernelError("rglru_scan: out is contiguous [T, W]")
+    with phase("scan"):
+        if chunked is None:
+            _i32(reqs, "reqs")
+            _check(lib().bg_rglru_scan(_p(gates), _p(u), _p(src), src.stride(0), y_col, _p(gate_bias_r), _p(gate_bias_i), _p(decay),
+                                       _p(state), state.stride(0), _p(slots), _p(reqs), n_req, _p(out), _dt(out), T, W, blocks,
+                                       _stream()), "rglru_scan")
+        else:
+            chunks, n_chunks, longs, n_long, chunk_rows = chunked
+            if n_chunks == 0:
+                return
+            pq = torch.empty((n_chunks, 2, W), dtype=torch.float32, device=u.device)
+            _check(lib().bg_rglru_scan_chunked(_p(gates), _p(u), _p(src), src.stride(0), y_col, _p(gate_bias_r), _p(gate_bias_i),
+                                               _p(decay), _p(state), state.stride(0), _p(slots), _p(chunks), n_chunks, _p(longs),
+                                               n_long, chunk_rows, _p(pq), _p(out), _dt(out), T, W, blocks, _stream()),
+                   "rglru_scan_chunked")
+            count_launches(2)
 
 
 def gemm_grouped(x: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, out: torch.Tensor, activation: str = "none",

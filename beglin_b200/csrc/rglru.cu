@@ -1,0 +1,219 @@
+// The real-gated linear recurrent unit: per channel c a state S_c that is carried from token to token,
+//
+//   r = sigmoid(gr + br),  i = sigmoid(gi + bi)        gr, gi: the gates' products of the convolved input u
+//   log a = -C r softplus(lam_c),  a = e^(log a)
+//   S <- a S + sqrt(1 - a^2) (i u),   out = S * gelu_tanh(y)      y: the other branch's product of the same token
+//
+// from S = 0 at a request's start (the first token is no special case).  Everything is float: the gates, the decay and
+// its logarithm, the step and the state; 1 - a^2 is formed as -expm1(2 log a), which does not cancel for a near one.
+//
+//   rglru_scan          one thread per (request, channel) walks the request's rows of the step in order from the state
+//                       in the request's slot and leaves the new state there.  Steps of single tokens and short portions.
+//   rglru_scan_chunked  long portions: the rows of a request are cut into chunks; S_end = P S_begin + Q with
+//                       P = prod a, Q the chunk's walk from zero, so (1) every (chunk, channel) forms P and Q, (2) a
+//                       thread per channel walks the chunks of a request to every chunk's starting state, (3) every
+//                       (chunk, channel) walks its rows again from that state and writes the outputs.  The two walks
+//                       differ from the plain one by rounding only.
+//
+// The gates' products come as [blocks][T][2 bs]: for channel c = b bs + o the recurrence gate at [b][t][o] and the
+// input gate at [b][t][bs + o].
+#include "common.cuh"
+
+namespace bg {
+
+constexpr int LRU_THREADS = 128;
+
+struct LruParams {
+    const float* gates;     // [blocks][T][2 bs]
+    const float* u;         // [T][W] the convolved input
+    const float* src;       // the input product's rows; y of channel c at src[t * src_stride + y_col + c]
+    int src_stride, y_col;
+    const float* br;        // [W] bias of the recurrence gate
+    const float* bi;        // [W] bias of the input gate
+    const float* sp;        // [W] C * softplus(lam), made once when the model is built
+    float* state;           // [slots][slot_stride], S in the first W values of a slot
+    long long slot_stride;
+    const int* slots;       // [requests]
+    const int* reqs;        // [n][3] = (request, first row, rows)
+    void* out;              // [T][W]
+    int T, W, bs;
+};
+
+__device__ __forceinline__ float sigmoid32(float v) { return 1.0f / (1.0f + expf(-v)); }
+__device__ __forceinline__ float gelu_tanh32(float z) {
+    return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+// (a, b) of S <- a S + b for row t of channel c.
+__device__ __forceinline__ void lru_step(const LruParams& p, size_t gate_at, int t, int c, float brc, float bic, float spc, float* a,
+                                         float* b) {
+    const float r = sigmoid32(p.gates[gate_at] + brc);
+    const float i = sigmoid32(p.gates[gate_at + p.bs] + bic);
+    const float log_a = -r * spc;
+    *a = expf(log_a);
+    *b = sqrtf(-expm1f(2.0f * log_a)) * (i * p.u[(size_t)t * p.W + c]);
+}
+
+template <typename TO>
+__global__ void __launch_bounds__(LRU_THREADS)
+rglru_scan_kernel(LruParams p) {
+    pdl_launch();
+    pdl_wait();
+    const int c = blockIdx.x * LRU_THREADS + threadIdx.x;
+    if (c >= p.W) return;
+    const int req = p.reqs[blockIdx.y * 3 + 0], row0 = p.reqs[blockIdx.y * 3 + 1], n = p.reqs[blockIdx.y * 3 + 2];
+    if (n <= 0) return;
+    const int blk = c / p.bs, o = c - blk * p.bs;
+    const float brc = p.br[c], bic = p.bi[c], spc = p.sp[c];
+    float* st = p.state + (size_t)p.slots[req] * p.slot_stride + c;
+    float S = *st;
+    TO* out = (TO*)p.out;
+    const size_t gbase = ((size_t)blk * p.T) * (2 * p.bs) + o;
+    for (int j = 0; j < n; ++j) {
+        const int t = row0 + j;
+        float a, b;
+        lru_step(p, gbase + (size_t)t * (2 * p.bs), t, c, brc, bic, spc, &a, &b);
+        S = fmaf(a, S, b);
+        out[(size_t)t * p.W + c] = from_float<TO>(S * gelu_tanh32(p.src[(size_t)t * p.src_stride + p.y_col + c]));
+    }
+    *st = S;
+}
+
+// chunks: [n][4] = (request, first row, rows, 0); longs: [n][4] = (request, first row, rows, index of its first chunk).
+// pq: [chunks][2][W] = (P, Q) of a chunk; after the walk, [chunk][0] is the state at the chunk's start.
+__global__ void __launch_bounds__(LRU_THREADS)
+rglru_chunk_sums_kernel(LruParams p, const int* __restrict__ chunks, float* __restrict__ pq) {
+    pdl_launch();
+    pdl_wait();
+    const int c = blockIdx.x * LRU_THREADS + threadIdx.x;
+    if (c >= p.W) return;
+    const int ch = blockIdx.y;
+    const int row0 = chunks[ch * 4 + 1], n = chunks[ch * 4 + 2];
+    const int blk = c / p.bs, o = c - blk * p.bs;
+    const float brc = p.br[c], bic = p.bi[c], spc = p.sp[c];
+    const size_t gbase = ((size_t)blk * p.T) * (2 * p.bs) + o;
+    float P = 1.0f, Q = 0.0f;
+    for (int j = 0; j < n; ++j) {
+        const int t = row0 + j;
+        float a, b;
+        lru_step(p, gbase + (size_t)t * (2 * p.bs), t, c, brc, bic, spc, &a, &b);
+        P *= a;
+        Q = fmaf(a, Q, b);
+    }
+    pq[((size_t)ch * 2 + 0) * p.W + c] = P;
+    pq[((size_t)ch * 2 + 1) * p.W + c] = Q;
+}
+
+__global__ void __launch_bounds__(LRU_THREADS)
+rglru_chunk_walk_kernel(LruParams p, const int* __restrict__ longs, int chunk_rows, float* __restrict__ pq) {
+    pdl_launch();
+    pdl_wait();
+    const int c = blockIdx.x * LRU_THREADS + threadIdx.x;
+    if (c >= p.W) return;
+    const int req = longs[blockIdx.y * 4 + 0], n = longs[blockIdx.y * 4 + 2], first = longs[blockIdx.y * 4 + 3];
+    const int n_chunks = (n + chunk_rows - 1) / chunk_rows;
+    float* st = p.state + (size_t)p.slots[req] * p.slot_stride + c;
+    float S = *st;
+    for (int k = 0; k < n_chunks; ++k) {
+        const size_t at = ((size_t)(first + k) * 2) * p.W + c;
+        const float P = pq[at], Q = pq[at + p.W];
+        pq[at] = S;
+        S = fmaf(P, S, Q);
+    }
+    *st = S;
+}
+
+template <typename TO>
+__global__ void __launch_bounds__(LRU_THREADS)
+rglru_chunk_out_kernel(LruParams p, const int* __restrict__ chunks, const float* __restrict__ pq) {
+    pdl_launch();
+    pdl_wait();
+    const int c = blockIdx.x * LRU_THREADS + threadIdx.x;
+    if (c >= p.W) return;
+    const int ch = blockIdx.y;
+    const int row0 = chunks[ch * 4 + 1], n = chunks[ch * 4 + 2];
+    const int blk = c / p.bs, o = c - blk * p.bs;
+    const float brc = p.br[c], bic = p.bi[c], spc = p.sp[c];
+    const size_t gbase = ((size_t)blk * p.T) * (2 * p.bs) + o;
+    TO* out = (TO*)p.out;
+    float S = pq[((size_t)ch * 2) * p.W + c];
+    for (int j = 0; j < n; ++j) {
+        const int t = row0 + j;
+        float a, b;
+        lru_step(p, gbase + (size_t)t * (2 * p.bs), t, c, brc, bic, spc, &a, &b);
+        S = fmaf(a, S, b);
+        out[(size_t)t * p.W + c] = from_float<TO>(S * gelu_tanh32(p.src[(size_t)t * p.src_stride + p.y_col + c]));
+    }
+}
+
+// sp[c] = scale * softplus(lam[c]), float: log(1 + e^x), as x for large x.
+template <typename TW>
+__global__ void rglru_softplus_kernel(const TW* __restrict__ lam, float scale, float* __restrict__ sp, int W) {
+    pdl_launch();
+    pdl_wait();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= W) return;
+    const float x = to_float(lam[c]);
+    sp[c] = scale * (x > 20.0f ? x : log1pf(expf(x)));
+}
+
+}  // namespace bg
+
+using namespace bg;
+
+static int lru_params(LruParams* p, const float* gates, const float* u, const float* src, int src_stride, int y_col, const float* br,
+                      const float* bi, const float* sp, float* state, long long slot_stride, const int* slots, void* out, int T,
+                      int W, int blocks) {
+    if (W <= 0 || blocks <= 0 || W % blocks != 0 || T <= 0) return BG_ERR_SHAPE;
+    p->gates = gates; p->u = u; p->src = src; p->src_stride = src_stride; p->y_col = y_col; p->br = br; p->bi = bi; p->sp = sp;
+    p->state = state; p->slot_stride = slot_stride; p->slots = slots; p->reqs = nullptr; p->out = out; p->T = T; p->W = W;
+    p->bs = W / blocks;
+    return BG_OK;
+}
+
+// The requests `reqs` [n_req][3] of a step walked row by row.
+extern "C" int bg_rglru_scan(const float* gates, const float* u, const float* src, int src_stride, int y_col, const float* br,
+                             const float* bi, const float* sp, float* state, long long slot_stride, const int* slots,
+                             const int* reqs, int n_req, void* out, int out_dtype, int T, int W, int blocks, cudaStream_t stream) {
+    if (n_req <= 0 || T <= 0) return BG_OK;
+    if (n_req > 65535) return BG_ERR_SHAPE;
+    LruParams p;
+    const int rc = lru_params(&p, gates, u, src, src_stride, y_col, br, bi, sp, state, slot_stride, slots, out, T, W, blocks);
+    if (rc != BG_OK) return rc;
+    p.reqs = reqs;
+    const dim3 grid((W + LRU_THREADS - 1) / LRU_THREADS, n_req);
+    BG_DISPATCH_DTYPE(out_dtype, TO, launch(rglru_scan_kernel<TO>, grid, dim3(LRU_THREADS), 0, stream, p));
+    BG_LAUNCH_CHECK();
+    return BG_OK;
+}
+
+// The long requests of a step in chunks of `chunk_rows` rows: chunks [n_chunks][4], longs [n_long][4], pq float
+// [n_chunks][2][W] of the caller's.
+extern "C" int bg_rglru_scan_chunked(const float* gates, const float* u, const float* src, int src_stride, int y_col,
+                                     const float* br, const float* bi, const float* sp, float* state, long long slot_stride,
+                                     const int* slots, const int* chunks, int n_chunks, const int* longs, int n_long,
+                                     int chunk_rows, float* pq, void* out, int out_dtype, int T, int W, int blocks,
+                                     cudaStream_t stream) {
+    if (n_chunks <= 0 || n_long <= 0 || T <= 0) return BG_OK;
+    if (n_chunks > 65535 || n_long > 65535 || chunk_rows <= 0) return BG_ERR_SHAPE;
+    LruParams p;
+    const int rc = lru_params(&p, gates, u, src, src_stride, y_col, br, bi, sp, state, slot_stride, slots, out, T, W, blocks);
+    if (rc != BG_OK) return rc;
+    const unsigned bx = (W + LRU_THREADS - 1) / LRU_THREADS;
+    launch(rglru_chunk_sums_kernel, dim3(bx, n_chunks), dim3(LRU_THREADS), 0, stream, p, chunks, pq);
+    BG_LAUNCH_CHECK();
+    launch(rglru_chunk_walk_kernel, dim3(bx, n_long), dim3(LRU_THREADS), 0, stream, p, longs, chunk_rows, pq);
+    BG_LAUNCH_CHECK();
+    BG_DISPATCH_DTYPE(out_dtype, TO, launch(rglru_chunk_out_kernel<TO>, dim3(bx, n_chunks), dim3(LRU_THREADS), 0, stream, p, chunks,
+                                            (const float*)pq));
+    BG_LAUNCH_CHECK();
+    return BG_OK;
+}
+
+extern "C" int bg_rglru_softplus(const void* lam, int lam_dtype, float scale, float* sp, int W, cudaStream_t stream) {
+    if (W <= 0) return BG_OK;
+    BG_DISPATCH_DTYPE(lam_dtype, TW, launch(rglru_softplus_kernel<TW>, dim3((W + 255) / 256), dim3(256), 0, stream, (const TW*)lam,
+                                            scale, sp, W));
+    BG_LAUNCH_CHECK();
+    return BG_OK;
+}

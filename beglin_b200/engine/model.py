@@ -109,13 +109,22 @@ class DecoderModel:
         stream = ResidualStream(x)
         if self.keep_origin:
             stream.origin = x.clone()
+        if self.spec.lanes:
+            stream.open_lanes(self.spec.lanes)
         for si, stage in enumerate(self.spec.order):
             if stage.enter is not None:
                 self.entries[stage.enter].forward(stream, batch)
             owner = si if stage.cache is None else stage.cache
             view = cache.view(owner, batch) if owner in cache.stage_group else None
             self.blocks[stage.layer].forward(stream, batch, view)
-            if tap is not None:
+            if tap is not None and stream.lanes is not None:
+                lanes = stream.lanes.clone()
+                if stream.lane_owed is not None:
+                    y, link = stream.lane_owed
+                    y = y.float().reshape(-1, *lanes.shape[1:]).sum(0)
+                    lanes = torch.einsum("ab,atd->btd", link.mix, lanes) + link.out[:, None, None] * y
+                tap(si, lanes.sum(0))
+            elif tap is not None:
                 rows = stream.x.clone()
                 if stream.pending is not None:
                     rows += stream.pending.float().reshape(-1, *rows.shape).sum(0)
@@ -125,8 +134,11 @@ class DecoderModel:
                 tap(si, rows)
         if batch.n_logit_rows == 0:
             return None
-        stream.settle()
-        h = self.final_norm.add_norm(stream.x, stream.pending, rows=batch.logit_rows, update=False)
+        if stream.lanes is not None:               # the final norm reads the sum of the lanes, at the wanted rows
+            h = self.final_norm.add_norm(stream.lane_sum(batch.logit_rows), None, update=False)
+        else:
+            stream.settle()
+            h = self.final_norm.add_norm(stream.x, stream.pending, rows=batch.logit_rows, update=False)
         logits = self.head(h, out_dtype=torch.float32)
         if self.spec.logit_softcap > 0.0:
             ops.softcap(logits, self.spec.logit_softcap)

@@ -1,7 +1,7 @@
 """The parts a model is put together from, and their registries.  Importing this package registers
 the built-in parts."""
-from . import (attention, block, decay_attention, depth, entry, latent_attention, mamba2, mlp, moe, norm, parallel,  # noqa: F401
-               rope)                                                                                               # (registration)
+from . import (attention, block, decay_attention, depth, entry, lanes, latent_attention, mamba2, mlp, moe, norm, parallel,  # noqa: F401
+               rglru, rope)                                                                                               # (registration)
 from .cache_need import CompositeNeed, FixedStateNeed, FixedStateView, PagedKVNeed, PagedKVView, PagedLatentNeed
 from .context import BuildContext
 from .linear import Linear

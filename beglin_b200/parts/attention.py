@@ -9,7 +9,8 @@ product.  All rows' keys and values are in the cache before any row's attention 
 
 Options of the spec, each off for the plain form: values of another size than keys; an RMS norm of the whole query
 row and of the whole key row of a token before the rotation, or of every head by itself; a softmax whose denominator is
-enlarged by one, or by exp of a learned number per head; scores squashed by c tanh(s / c); a gate, sigmoid of a further
+enlarged by one, or by exp of a learned number per head; scores squashed by c tanh(s / c); queries that see the keys of their
+own block of positions only; a gate, sigmoid of a further
 product of the mixer's input, on the joined heads before the output product, feature by feature or one number per head.  The gate's matrix is
 one more block of rows of the one q/k/v product.  With any of the first two the kernel that norms, rotates and appends
 is `qk_norm_rope_append`.
@@ -84,9 +85,9 @@ class GQAAttention:
             return None
         stored = GQAAttention.stored_head(spec, ctx)
         if stored is not None:
-            return PagedKVNeed(spec.n_kv_heads, stored, spec.window)
+            return PagedKVNeed(spec.n_kv_heads, stored, spec.window, None, spec.block)
         return PagedKVNeed(spec.n_kv_heads, spec.head_dim, spec.window,
-                           None if spec.value_dim == spec.head_dim else spec.value_dim)
+                           None if spec.value_dim == spec.head_dim else spec.value_dim, spec.block)
 
     def __init__(self, spec: AttentionSpec, tensors: Dict[str, torch.Tensor], ctx: BuildContext):
         if spec.n_heads % spec.n_kv_heads:
@@ -139,7 +140,10 @@ class GQAAttention:
         self.plans = {d: ops.attention_plan(self.nh // self.nkv, khd, ctx.cache_dtype, d, ctx.attention,
                                             ctx.page_size, vd=kvd_, softcap=self.score_cap > 0.0,
                                             learned_sink=self.sink_weight is not None) for d in (False, True)}
-        self.window = int(spec.window) if spec.window else 0
+        if spec.block is not None and (spec.window is not None or spec.block <= 0):
+            raise ValueError("blocks of positions stand in place of a window and hold at least one position")
+        # what the kernels are told: a positive number is a sliding window, a negative one the size of the blocks
+        self.window = int(spec.window) if spec.window else (-int(spec.block) if spec.block else 0)
         # the fused q/k/v product can rotate and append itself: whole heads rotated in halves, a cache of its own
         # in bfloat16
         self.rope_in_product = (spec.own_kv and self.position.rotary_dim == self.hd and not self.position.interleaved

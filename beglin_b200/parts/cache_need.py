@@ -15,11 +15,13 @@ import torch
 @dataclass(frozen=True)
 class PagedKVNeed:
     """Keys and values of every position (window None) or of the last `window` positions.  `v_head_dim` is given
-    when values have another size than keys."""
+    when values have another size than keys.  `block` b: a query reads only the positions of its own block of b positions
+    (blocks counted from position 0), so the pages wholly in front of the newest block are given back."""
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     v_head_dim: Optional[int] = None
+    block: Optional[int] = None
 
     def page_shape(self, page_size: int) -> Tuple[int, ...]:
         """What one page of one stage holds: (2 = keys, values; kv heads; positions; features); with values of
@@ -36,6 +38,7 @@ class PagedLatentNeed:
     its keys and values from a low-rank projection, with whatever rides along, such as a rotated key part)."""
     width: int
     window: Optional[int] = None
+    block: Optional[int] = None
 
     def page_shape(self, page_size: int) -> Tuple[int, ...]:
         return (page_size, self.width)

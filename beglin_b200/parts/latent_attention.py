@@ -14,7 +14,8 @@ ONE kernel for the norm of the query latent and the norm, rotation and append of
 query product; queries into the latent space; attention (the queries' rotated part turned inside the kernel)
 and the merge of its splits; values out of the latent space; gates; the output product, which in steps of
 few rows adds into the residual stream itself.  A mixer with `own_kv` False has no key/value projection and
-reads the cache of the stage it is told to.
+reads the cache of the stage it is told to.  Options of the spec: queries that are one product of the input (no query
+latent), no rotated part, no gates, a sliding window.
 
 Long prompt portions in bfloat16 go the other way round where the sizes allow it (dim + rot_dim = vdim = 64 or
 128): the keys and values of all heads are made once per step from the request's cached rows, by ONE product
@@ -44,12 +45,15 @@ class LatentAttention:
     @staticmethod
     def expected_tensors(spec: LatentAttentionSpec) -> List[TensorRole]:
         H, qd = spec.n_heads, spec.dim + spec.rot_dim
-        roles = [TensorRole("q_down.weight", (spec.q_rank, spec.hidden), True, True),
-                 TensorRole("q_down.norm", (spec.q_rank,), role="scale"),
-                 TensorRole("q_up.weight", (H * qd, spec.q_rank), True, True),
-                 TensorRole("k_up.weight", (H * spec.dim, spec.kv_rank), True, True),
-                 TensorRole("v_up.weight", (H * spec.vdim, spec.kv_rank), True, True),
-                 TensorRole("o_proj.weight", (spec.hidden, H * spec.vdim), True, True)]
+        if spec.q_rank is None:                     # queries straight from the mixer's input
+            roles = [TensorRole("q_proj.weight", (H * qd, spec.hidden), True, True)]
+        else:
+            roles = [TensorRole("q_down.weight", (spec.q_rank, spec.hidden), True, True),
+                     TensorRole("q_down.norm", (spec.q_rank,), role="scale"),
+                     TensorRole("q_up.weight", (H * qd, spec.q_rank), True, True)]
+        roles += [TensorRole("k_up.weight", (H * spec.dim, spec.kv_rank), True, True),
+                  TensorRole("v_up.weight", (H * spec.vdim, spec.kv_rank), True, True),
+                  TensorRole("o_proj.weight", (spec.hidden, H * spec.vdim), True, True)]
         if spec.own_kv:
             roles += [TensorRole("kv_down.weight", (spec.kv_rank + spec.rot_dim, spec.hidden), True, True),
                       TensorRole("kv_down.norm", (spec.kv_rank,), role="scale")]
@@ -61,7 +65,7 @@ class LatentAttention:
     def cache_need(spec: LatentAttentionSpec) -> Optional[PagedLatentNeed]:
         if not spec.own_kv:
             return None
-        return PagedLatentNeed(spec.kv_rank + spec.rot_dim)
+        return PagedLatentNeed(spec.kv_rank + spec.rot_dim, spec.window)
 
     def __init__(self, spec: LatentAttentionSpec, tensors: Dict[str, torch.Tensor], ctx: BuildContext):
         self.spec, self.ctx = spec, ctx
@@ -72,17 +76,23 @@ class LatentAttention:
             raise ValueError(f"the rotated part of {spec.rot_dim} features turns in neighbouring pairs over at most "
                              f"its own width, not {self.rot_dims} features paired '{spec.position.pairing}'")
         # the products of the mixer's input, as ONE: [query latent | key/value latent, key part | gates]
-        names = ["q_down.weight"] + (["kv_down.weight"] if spec.own_kv else []) + (["gate.weight"] if spec.gated else [])
+        self.direct_q = spec.q_rank is None
+        if self.direct_q and not spec.own_kv:
+            raise ValueError("latent attention without a query latent has a key/value latent of its own")
+        self.q_rank = 0 if self.direct_q else int(spec.q_rank)
+        self.window = int(spec.window) if spec.window else 0
+        names = ([] if self.direct_q else ["q_down.weight"]) + (["kv_down.weight"] if spec.own_kv else []) \
+            + (["gate.weight"] if spec.gated else [])
         w_down = torch.cat([tensors[n] for n in names], dim=0)
         if w_down.shape[0] % 16:                    # rows of zeros up to a multiple of 16 outputs: a width that is no multiple
             pad = 16 - w_down.shape[0] % 16         # of 8 takes the library's product of many rows off its fast kernels
             w_down = torch.cat([w_down, torch.zeros((pad, w_down.shape[1]), dtype=w_down.dtype, device=w_down.device)], dim=0)
         self.down = Linear(w_down, None, ctx, label="proj_qkv")
-        self.kv_col = spec.q_rank
-        self.gate_col = spec.q_rank + (spec.kv_rank + spec.rot_dim if spec.own_kv else 0)
-        self.q_norm = ctx.vector(tensors["q_down.norm"])
+        self.kv_col = self.q_rank
+        self.gate_col = self.q_rank + (spec.kv_rank + spec.rot_dim if spec.own_kv else 0)
+        self.q_norm = None if self.direct_q else ctx.vector(tensors["q_down.norm"])
         self.kv_norm = ctx.vector(tensors["kv_down.norm"]) if spec.own_kv else None
-        self.q_up = Linear(tensors["q_up.weight"], None, ctx, label="proj_q")
+        self.q_up = Linear(tensors["q_proj.weight" if self.direct_q else "q_up.weight"], None, ctx, label="proj_q")
         # per head: W_uk^T as [kv_rank, dim] (the product into the latent space is x W^T with W = W_uk^T) and
         # W_uv as [vdim, kv_rank]
         self.k_up_t = ctx.matrix(tensors["k_up.weight"].reshape(H, spec.dim, spec.kv_rank).transpose(1, 2))
@@ -131,10 +141,14 @@ class LatentAttention:
         """The gated heads [T, H vdim] of a portion of ONE request, through keys and values made per head."""
         s, ctx = self.spec, self.ctx
         T, H, hd = batch.n_rows, s.n_heads, s.dim + s.rot_dim
-        S = batch.max_position + 1                                      # every position the portion's rows may see
+        # every position the portion's rows may see, from the page in which the first row's window begins
+        first = 0
+        if self.window and batch.starts is not None:                    # (a replayed graph does not know where it stands)
+            first = max(0, batch.starts[0] - self.window + 1) // 64 * 64
+        S = batch.max_position + 1 - first
         lat = torch.empty((S, s.kv_rank), dtype=torch.bfloat16, device=q.device)
-        kr = torch.empty((S, s.rot_dim), dtype=torch.bfloat16, device=q.device)
-        ops.latent_gather(cache.pool, cache.block_table, 0, s.kv_rank, lat, kr)
+        kr = torch.empty((S, max(s.rot_dim, 8)), dtype=torch.bfloat16, device=q.device)[:, :s.rot_dim]
+        ops.latent_gather(cache.pool, cache.block_table, 0, s.kv_rank, lat, kr, first=first)
         with ops.phase("kv_expand"):
             kv = torch.mm(lat, self.kv_up.t())                          # [S, H dim | H vdim]
         pages = torch.empty((-(-S // 64), 2, H, 64, hd), dtype=torch.bfloat16, device=q.device)
@@ -142,11 +156,11 @@ class LatentAttention:
         ops.latent_expand(kv, kr, H, s.dim, pages)
         if self.rot_dims:
             ops.rotate_q(q, H, hd, s.dim, self.rot_dims, cos_sin)
-        table = torch.arange(pages.shape[0], dtype=torch.int32, device=q.device).view(1, -1)
+        table = torch.arange(-(first // 64), pages.shape[0], dtype=torch.int32, device=q.device).clamp_(min=-1).view(1, -1)
         bq, tile = self.expand
         qblk, n_qblk = batch.query_blocks(bq)
         att = torch.empty((T, H * hd), dtype=torch.bfloat16, device=q.device)
-        ops.attention(q, q.stride(0), pages, table, batch.positions, qblk, n_qblk, batch.max_position, T, H, H, hd, 0,
+        ops.attention(q, q.stride(0), pages, table, batch.positions, qblk, n_qblk, batch.max_position, T, H, H, hd, self.window,
                       ctx.kv_split, tile, bq, self.scale, att, ctx.status, "tc_rows")
         if not s.gated:
             return att
@@ -165,14 +179,19 @@ class LatentAttention:
         T, H = batch.n_rows, s.n_heads
         down = self.down(h, out_dtype=torch.float32)                    # [T, q_rank (+ kv_rank + rot) (+ H)]
         cos_sin = self.position.table(batch) if self.rot_dims else None
-        cq = torch.empty((T, s.q_rank), dtype=ctx.compute_dtype, device=h.device)
-        if s.own_kv:                                                    # both norms of the product's rows in one launch
+        if self.direct_q:
             ops.latent_append(down, self.kv_col, s.kv_rank, s.rot_dim, self.rot_dims, self.kv_norm, s.eps, cos_sin,
-                              batch.positions, batch.row_req, cache.block_table, cache.pool, ctx.status,
-                              q_norm=(0, self.q_norm, cq))
+                              batch.positions, batch.row_req, cache.block_table, cache.pool, ctx.status)
+            q = self.q_up(h)                                            # [T, H (dim + rot)] straight from the input
         else:
-            ops.rmsnorm_slice(down, 0, s.q_rank, self.q_norm, s.eps, cq)
-        q = self.q_up(cq)                                               # [T, H (dim + rot)]
+            cq = torch.empty((T, s.q_rank), dtype=ctx.compute_dtype, device=h.device)
+            if s.own_kv:                                                # both norms of the product's rows in one launch
+                ops.latent_append(down, self.kv_col, s.kv_rank, s.rot_dim, self.rot_dims, self.kv_norm, s.eps, cos_sin,
+                                  batch.positions, batch.row_req, cache.block_table, cache.pool, ctx.status,
+                                  q_norm=(0, self.q_norm, cq))
+            else:
+                ops.rmsnorm_slice(down, 0, s.q_rank, self.q_norm, s.eps, cq)
+            q = self.q_up(cq)                                           # [T, H (dim + rot)]
         if self.expand is not None and batch.n_req == 1 and T >= self.EXPAND_ROWS:
             return self._result(self._per_head_keys(q, down, cos_sin, batch, cache), stream)
         q_plain = q.view(T, H, s.dim + s.rot_dim)[:, :, :s.dim].transpose(0, 1)          # [H, T, dim]
@@ -188,7 +207,7 @@ class LatentAttention:
         o_lat = torch.empty((H, T, s.kv_rank), dtype=ctx.compute_dtype, device=h.device)
         ops.latent_attention(q_lat, q, s.dim, s.rot_dim, self.rot_dims, cos_sin, cache.pool, cache.block_table,
                              batch.positions, qblk, n_qblk, batch.max_position, bq, hc, self.tile, split,
-                             self.scale, o_lat, ctx.status, mma_stages=stages)
+                             self.scale, o_lat, ctx.status, mma_stages=stages, window=self.window)
         v = self._per_head(o_lat, self.v_up, ctx.compute_dtype)        # [H, T, vdim]
         out = torch.empty((T, H * s.vdim), dtype=ctx.compute_dtype, device=h.device)
         if s.gated:

@@ -1,5 +1,5 @@
 """RMSNorm: y = x / sqrt(mean(x^2) + eps) * weight, statistics in float, eps inside the root, the
-weight multiplying directly (qwen_infer.c:711-714).  The residual add that precedes a norm is fused
+weight multiplying directly (qwen_infer.c:711-714), or, with the spec's `offset`, offset + weight.  The residual add that precedes a norm is fused
 into it: `add_norm` first does x += delta.  LayerNorm is the same with the mean taken off first and
 the variance in place of the mean square; it has a scale vector and no shift."""
 from __future__ import annotations
@@ -18,11 +18,21 @@ from .spec import NormSpec, TensorRole
 class RMSNorm:
     @staticmethod
     def expected_tensors(spec: NormSpec) -> List[TensorRole]:
-        return [TensorRole("weight", (spec.size,), role="scale")]
+        return [TensorRole("weight", (spec.size,), role="vector" if spec.offset else "scale")]
 
     def __init__(self, spec: NormSpec, tensors: Dict[str, torch.Tensor], ctx: BuildContext):
         self.spec, self.ctx = spec, ctx
-        self.weight = ctx.vector(tensors["weight"])
+        if spec.offset:                    # a weight stored around zero: offset + w, formed in float and kept so
+            self.weight = (tensors["weight"].to(device=ctx.device, dtype=torch.float32) + float(spec.offset)).contiguous()
+        else:
+            self.weight = ctx.vector(tensors["weight"])
+        self._weight_f32 = None
+
+    def weight_f32(self) -> torch.Tensor:
+        """The multiplying weight as float32 (for kernels that norm in float from float weights)."""
+        if self._weight_f32 is None:
+            self._weight_f32 = self.weight if self.weight.dtype == torch.float32 else self.weight.float().contiguous()
+        return self._weight_f32
 
     def add_norm(self, x: torch.Tensor, delta: Optional[torch.Tensor], rows: Optional[torch.Tensor] = None,
                  update: bool = True) -> torch.Tensor:

@@ -15,6 +15,7 @@ POSITIONS: Dict[str, type] = {}
 BLOCKS: Dict[str, type] = {}
 COMBINERS: Dict[str, type] = {}      # what a block does to the stream behind its sublayers (depth averages)
 ENTRIES: Dict[str, type] = {}        # what rewrites the stream in front of a stage (the input of a pass of a loop)
+LINKS: Dict[str, type] = {}          # how a sublayer reads from and writes to a residual kept in several lanes
 
 
 def _register(table: Dict[str, type], what: str) -> Callable[[str], Callable[[type], type]]:
@@ -34,6 +35,7 @@ register_position = _register(POSITIONS, "position encoding")
 register_block = _register(BLOCKS, "block")
 register_combiner = _register(COMBINERS, "combiner")
 register_entry = _register(ENTRIES, "entry")
+register_link = _register(LINKS, "link")
 
 
 def lookup(table: Dict[str, type], kind: str, what: str) -> type:
@@ -69,7 +71,7 @@ def block_class(kind: str) -> type:
 
 
 FAMILIES = {"mixer": (MIXERS, "mixer"), "feed_forward": (FEED_FORWARDS, "feed-forward"), "norm": (NORMS, "norm"),
-            "combiner": (COMBINERS, "combiner")}
+            "combiner": (COMBINERS, "combiner"), "link": (LINKS, "link")}
 
 
 def part_class(family: str, kind: str) -> type:

@@ -33,10 +33,12 @@ class TensorRole:
 @dataclass(frozen=True)
 class NormSpec:
     """kind "rmsnorm": x * rsqrt(mean(x^2) + eps) * w.  kind "layernorm": centred first,
-    c = x - mean(x), then c * rsqrt(mean(c^2) + eps) * w; there is no shift vector."""
+    c = x - mean(x), then c * rsqrt(mean(c^2) + eps) * w; there is no shift vector.  `offset` o (rmsnorm): the stored
+    weight lies around zero and the rows are multiplied by o + w, the sum formed in float."""
     size: int
     eps: float
     kind: str = "rmsnorm"
+    offset: float = 0.0
 
 
 @dataclass(frozen=True)
@@ -73,7 +75,8 @@ class AttentionSpec:
     product gives ONE number per query head, whose sigmoid multiplies the head's result.  `qk_norm` "head": every head of
     the queries and of the keys is RMS-normed by itself, with one weight vector of head_dim values for all query heads and one
     for all key heads.  `sink` "learned": the extra key's score is a learned number per query head (tensor `sink`) in place
-    of 0.  `score_cap` c: a scaled score s becomes c tanh(s / c) before the softmax."""
+    of 0.  `score_cap` c: a scaled score s becomes c tanh(s / c) before the softmax.  `block` b (in place of a window): a query
+    at position i sees the keys j <= i with floor(j / b) = floor(i / b), blocks counted from position 0 of the sequence."""
     hidden: int
     n_heads: int
     n_kv_heads: int
@@ -90,6 +93,7 @@ class AttentionSpec:
     sink: object = False                   # False, True (a key of score 0) or "learned" (a score per query head)
     gate: Optional[str] = None             # None, "elementwise" or "head"
     score_cap: Optional[float] = None      # None: scores as they are
+    block: Optional[int] = None            # None: no blocks of positions
     kind: str = "gqa_attention"
 
     @property
@@ -112,7 +116,14 @@ class RoutedExpertsSpec:
     is down(act(up(h))) without a gate branch and without biases; `activation` "relu2" is the square of relu.
     `router_activation` "sigmoid": the scores are sigmoid of the router's logits, which are computed in 32-bit.
     `renormalize`: whether the chosen scores are divided by their sum.  `scale_input`: the score multiplies the
-    expert's input (True) or its output (False)."""
+    expert's input (True) or its output (False).
+
+    `activation` "glu_clamped": an expert has a gate branch, down(g sigmoid(1.702 g) (u + 1)) with g = min(gate(h), `limit`)
+    and u = clamp(up(h), -limit, limit).  `router_activation` "softmax": the scores are the softmax of the logits over all
+    router outputs.  `choice_bias`: a learned number per router output (tensor `router.bias`) is added to the scores when
+    the experts are chosen, and plays no part in the weights.  `route_scale` multiplies the weights.  `identity` n: the
+    router has `experts` + n outputs, and the last n stand for experts without weights that return their input.
+    `shared`: an expert that every token passes, added to the sum."""
     hidden: int
     intermediate: int
     experts: int
@@ -121,6 +132,11 @@ class RoutedExpertsSpec:
     router_activation: str = "sigmoid"
     renormalize: bool = False
     scale_input: bool = True
+    limit: float = 0.0
+    choice_bias: bool = False
+    route_scale: float = 1.0
+    identity: int = 0
+    shared: Optional[SharedExpertSpec] = None
     kind: str = "routed_experts"
 
 
@@ -131,19 +147,22 @@ class LatentAttentionSpec:
     heads; values of `vdim` features; the queries pass a latent of `q_rank` features, keys and values one of
     `kv_rank`.  `position.rotary_dim` leading features of the rot part turn.  Each head's result is scaled by
     sigmoid of a per-head gate read from the mixer's input when `gated`.  `own_kv` False: no down-projection
-    of its own; the latent and key part of another stage's cache are read."""
+    of its own; the latent and key part of another stage's cache are read.  `q_rank` None: the queries are one product
+    of the mixer's input (tensor `q_proj.weight`), without a latent of their own.  `rot_dim` 0: no rotated part at all.
+    `window` w: a query sees itself and the w - 1 positions before it."""
     hidden: int
     n_heads: int
     dim: int
     rot_dim: int
     vdim: int
-    q_rank: int
+    q_rank: Optional[int]
     kv_rank: int
     scale: float
     eps: float
     position: PositionSpec
     gated: bool = True
     own_kv: bool = True
+    window: Optional[int] = None
     kind: str = "latent_attention"
 
 
@@ -196,6 +215,38 @@ class InputMixSpec:
     [hidden, 2 hidden] (the stream's half first)."""
     hidden: int
     kind: str = "input_mix"
+
+
+@dataclass(frozen=True)
+class RGLRUSpec:
+    """A recurrent block around a real-gated linear recurrent unit.  Two branches of `width` channels: y = gelu_tanh(W_y h +
+    b_y), and u = the causal convolution per channel (`conv` taps, a bias, no activation) of W_x h + b_x.  u is cut into
+    `blocks` equal parts; in part b, r = sigmoid(A_b u_b + a_b) and i = sigmoid(B_b u_b + b_b) with square matrices.  Per
+    channel log a = -`decay_scale` r softplus(lam), S <- a S + sqrt(1 - a^2) (i u) from S = 0 at a request's start, and the
+    result is W_o (S * y)."""
+    hidden: int
+    width: int
+    blocks: int
+    conv: int
+    decay_scale: float = 8.0
+    kind: str = "rglru"
+
+
+@dataclass(frozen=True)
+class LaneLinkSpec:
+    """How a sublayer is tied to a residual kept in `lanes` copies: it reads sum_a in[a] lane_a, and its result y replaces
+    every lane at once, lane_b <- sum_a mix[a, b] lane_a + out[b] y."""
+    lanes: int
+    kind: str = "lane_link"
+
+
+@dataclass(frozen=True)
+class SharedExpertSpec:
+    """An expert of the routed experts' form that every token passes; its result is multiplied by sigmoid of one number per
+    token, a product of the feed-forward's input, when `gated`."""
+    intermediate: int
+    limit: float
+    gated: bool = True
 
 
 @dataclass(frozen=True)
@@ -290,5 +341,7 @@ class ModelSpec:
     head_bias_name: Optional[str] = None  # a bias [vocab] added to the logits
     logit_softcap: float = 0.0            # c > 0: logits = c * tanh(logits / c)
     eos_ids: Tuple[int, ...] = ()
+    lanes: int = 0                        # n > 0: the residual is kept in n lanes, all equal to the embedded rows at the start;
+    #                                       the final norm reads their sum (blocks of a "lanes" kind tie the sublayers to them)
     extra: Dict[str, object] = field(default_factory=dict)
     entries: List[EntrySpec] = field(default_factory=list)   # parts that stages name in `enter`

@@ -43,6 +43,45 @@ class ResidualStream:
         self.terms: Optional[Terms] = None             # not yet added to x either: results with constants of their own
         #                                                (a block that adds scaled sums; whoever reads x calls settle())
         self.origin: Optional[torch.Tensor] = None     # float32 [T, d]: the embedded rows, kept for parts that mix them in
+        self.lanes: Optional[torch.Tensor] = None      # float32 [n, T, d]: the residual as n lanes (then x is not the residual)
+        self.lane_owed = None                          # (result, link) of the last sublayer, not yet written to the lanes
+
+    # ------------------------------------------------------------------ a residual kept in lanes
+    def open_lanes(self, n: int) -> None:
+        """Every lane starts as a copy of x."""
+        from ..csrc import ops
+        self.lanes = torch.empty((n,) + tuple(self.x.shape), dtype=torch.float32, device=self.x.device)
+        ops.lane_fill(self.x, self.lanes)
+        self.lane_owed = None
+
+    def _owed_args(self) -> dict:
+        if self.lane_owed is None:
+            return {}
+        y, link = self.lane_owed
+        return {"owed": y, "mix": link.mix, "out_weights": link.out}
+
+    def lane_read(self, link, norm, dtype: torch.dtype) -> torch.Tensor:
+        """What a sublayer tied by `link` reads, RMS-normed by `norm`, in `dtype`; the last sublayer's result is written
+        to the lanes in the same pass."""
+        from ..csrc import ops
+        h = torch.empty(self.x.shape, dtype=dtype, device=self.x.device)
+        ops.lane_step(self.lanes, in_weights=link.inw, norm_weight=norm.weight_f32(), eps=norm.spec.eps, h=h, **self._owed_args())
+        self.lane_owed = None
+        return h
+
+    def lane_owe(self, y: torch.Tensor, link) -> None:
+        self.lane_owed = (y, link)
+
+    def lane_sum(self, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """The sum of the lanes, float32, with what is owed counted in: of all rows (the lanes are then brought up to
+        date) or of `rows` only (they are left as they are)."""
+        from ..csrc import ops
+        n = self.x.shape[0] if rows is None else rows.numel()
+        z = torch.empty((n, self.x.shape[1]), dtype=torch.float32, device=self.x.device)
+        ops.lane_step(self.lanes, z=z, rows=rows, **self._owed_args())
+        if rows is None:
+            self.lane_owed = None
+        return z
 
     def settle(self) -> None:
         """Adds the scaled terms that are still owed to x (the blocks that leave such terms fold the sum into their own
