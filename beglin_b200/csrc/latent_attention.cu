@@ -167,7 +167,7 @@ latent_attention_partial_kernel(LatentParams p) {
         for (int j = tid; j < tile; j += LAT_THREADS) {
             const int key = t0 + j;
             long long off = -1;
-            if (key < k_end) {
+            if (key >= lo_first && key < k_end) {      // (a key in front of every row's window may lie in a page given back)
                 const int page = p.block_table[(size_t)req * p.max_pages + key / p.page_size];
                 if (page < 0 || page >= p.num_pages) {
                     if (p.status) atomicOr(p.status, BG_STATUS_BAD_PAGE);

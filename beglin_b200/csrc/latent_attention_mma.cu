@@ -155,7 +155,7 @@ latent_attention_mma_kernel(LatentMmaParams p) {
         const int key = t0 + j;
         bool ok = false;
         const __nv_bfloat16* src = nullptr;
-        if (key < k_end) {
+        if (key >= lo_first && key < k_end) {          // (a key in front of every row's window may lie in a page given back)
             const int page = p.block_table[(size_t)req * p.max_pages + key / p.page_size];
             if (page < 0 || page >= p.num_pages) {
                 if (p.status && c0 == 0) atomicOr(p.status, BG_STATUS_BAD_PAGE);

@@ -30,7 +30,7 @@ struct RouteRule {
 
 // One warp chooses for one token: `sc` holds the token's E logits in shared memory and is used up.  Without a bias and
 // without the softmax the choice is made on the logits: sigmoid keeps their order, but rounds large ones to the same
-// score.  Otherwise it is made on score + bias, the scores formed anew from the logits each round; a logit of -inf marks
+// score.  Otherwise it is made on score + bias, the scores formed anew from the logits each time; a logit of -inf marks
 // an expert that is taken.  Ties go to the lower index.
 __device__ __forceinline__ void choose_experts(float* sc, int E, int top, RouteRule rule, int* __restrict__ ids,
                                                float* __restrict__ weights, size_t t, int lane) {
