@@ -255,17 +255,21 @@ __global__ void route_combine_kernel(const TY* __restrict__ yp, const float* __r
 // The same sum for a layer that also has experts without weights and a shared expert:
 //   out[t] = sum_j w_j (id_j < n_real ? yp[row_of[t top + j]] : h[t])  +  sigmoid(sg[t]) shared[t].
 // An expert whose index is n_real or more returns its input (the step's rows h in the compute type).  `shared` [T][d]
-// float is the result of an expert that every token passes, `sg` one number per token (element t at sg[t * sg_stride]),
-// whose sigmoid multiplies it; without `sg` the shared result is added as it is.  Ranks in index order, float.
+// float is the result of an expert that every token passes, `sg` one number per token (element t at sg[t * sg_stride], float
+// or bfloat16), whose sigmoid multiplies it; without `sg` the shared result is added as it is.  Ranks in index order, float.
 template <typename TY, typename TH>
 __global__ void route_combine_ext_kernel(const TY* __restrict__ yp, const float* __restrict__ weights, const int* __restrict__ row_of,
                                          const int* __restrict__ ids, int n_real, const TH* __restrict__ h, int ldh,
-                                         const float* __restrict__ shared, const float* __restrict__ sg, int sg_stride,
+                                         const float* __restrict__ shared, const void* __restrict__ sg, int sg_float, int sg_stride,
                                          float* __restrict__ out, int T, int d, int top) {
     pdl_launch();
     pdl_wait();
     const int t = blockIdx.x;
-    const float sgate = shared ? (sg ? 1.0f / (1.0f + expf(-sg[(size_t)t * sg_stride])) : 1.0f) : 0.0f;
+    float sgate = shared ? 1.0f : 0.0f;
+    if (shared && sg) {
+        const float z = sg_float ? ((const float*)sg)[(size_t)t * sg_stride] : __bfloat162float(((const __nv_bfloat16*)sg)[(size_t)t * sg_stride]);
+        sgate = 1.0f / (1.0f + expf(-z));
+    }
     for (int i = threadIdx.x; i < d; i += blockDim.x) {
         float acc = 0.0f;
         for (int j = 0; j < top; ++j) {
@@ -275,6 +279,42 @@ __global__ void route_combine_ext_kernel(const TY* __restrict__ yp, const float*
         }
         if (shared) acc = fmaf(sgate, shared[(size_t)t * d + i], acc);
         out[(size_t)t * d + i] = acc;
+    }
+}
+
+// The same, four columns a thread (d a multiple of 4, float results of the experts, 16-byte aligned rows).
+template <typename TH>
+__global__ void route_combine_ext_vec4_kernel(const float* __restrict__ yp, const float* __restrict__ weights,
+                                              const int* __restrict__ row_of, const int* __restrict__ ids, int n_real,
+                                              const TH* __restrict__ h, int ldh, const float* __restrict__ shared,
+                                              const void* __restrict__ sg, int sg_float, int sg_stride, float* __restrict__ out, int T,
+                                              int d, int top) {
+    pdl_launch();
+    pdl_wait();
+    const int t = blockIdx.x;
+    float sgate = shared ? 1.0f : 0.0f;
+    if (shared && sg) {
+        const float z = sg_float ? ((const float*)sg)[(size_t)t * sg_stride] : __bfloat162float(((const __nv_bfloat16*)sg)[(size_t)t * sg_stride]);
+        sgate = 1.0f / (1.0f + expf(-z));
+    }
+    for (int i = threadIdx.x * 4; i < d; i += blockDim.x * 4) {
+        float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        float4 hv;
+        {
+            const TH* hp = h + (size_t)t * ldh + i;
+            hv = make_float4(to_float(hp[0]), to_float(hp[1]), to_float(hp[2]), to_float(hp[3]));
+        }
+        for (int j = 0; j < top; ++j) {
+            const int a = t * top + j;
+            const float w = weights[a];
+            const float4 v = ids[a] < n_real ? *reinterpret_cast<const float4*>(yp + (size_t)row_of[a] * d + i) : hv;
+            acc.x = fmaf(w, v.x, acc.x); acc.y = fmaf(w, v.y, acc.y); acc.z = fmaf(w, v.z, acc.z); acc.w = fmaf(w, v.w, acc.w);
+        }
+        if (shared) {
+            const float4 s = *reinterpret_cast<const float4*>(shared + (size_t)t * d + i);
+            acc.x = fmaf(sgate, s.x, acc.x); acc.y = fmaf(sgate, s.y, acc.y); acc.z = fmaf(sgate, s.z, acc.z); acc.w = fmaf(sgate, s.w, acc.w);
+        }
+        *reinterpret_cast<float4*>(out + (size_t)t * d + i) = acc;
     }
 }
 
@@ -293,6 +333,29 @@ __global__ void glu_clamped_kernel(const TI* __restrict__ gu, int ld, TO* __rest
     const float g = fminf(to_float(gu[r * ld + i]), limit);
     const float u = fminf(fmaxf(to_float(gu[r * ld + n + i]), -limit), limit);
     out[idx] = from_float<TO>(g / (1.0f + expf(-alpha * g)) * (u + 1.0f));
+}
+
+// The same, eight columns a thread (n and ld multiples of 8, 16-byte aligned rows).
+template <typename TI, typename TO>
+__global__ void glu_clamped_vec8_kernel(const TI* __restrict__ gu, int ld, TO* __restrict__ out, size_t total8, int n, float limit,
+                                        float alpha) {
+    pdl_launch();
+    pdl_wait();
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total8) return;
+    const int n8 = n >> 3;
+    const size_t r = idx / n8;
+    const int i = (int)(idx - r * n8) * 8;
+    float g[8], u[8];
+    load8(gu + r * ld + i, g);
+    load8(gu + r * ld + n + i, u);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        const float gg = fminf(g[e], limit);
+        const float uu = fminf(fmaxf(u[e], -limit), limit);
+        g[e] = gg / (1.0f + expf(-alpha * gg)) * (uu + 1.0f);
+    }
+    store8(out + r * n + i, g);
 }
 
 // ------------------------------------------------------------------------------------------------ grouped product
@@ -504,14 +567,23 @@ extern "C" int bg_route_combine(const void* yp, int y_dtype, const float* weight
 }
 
 extern "C" int bg_route_combine_ext(const void* yp, int y_dtype, const float* weights, const int* row_of, const int* ids, int n_real,
-                                    const void* h, int h_dtype, int ldh, const float* shared, const float* sg, int sg_stride,
-                                    float* out, int T, int d, int top, cudaStream_t stream) {
+                                    const void* h, int h_dtype, int ldh, const float* shared, const void* sg, int sg_dtype,
+                                    int sg_stride, float* out, int T, int d, int top, cudaStream_t stream) {
+    const int sg_float = sg_dtype == BG_DTYPE_F32 ? 1 : 0;
     if (T <= 0) return BG_OK;
     if (!ids || !h || top <= 0) return BG_ERR_SHAPE;
     const int threads = d >= 256 ? 256 : ((d + 31) / 32) * 32;
+    if (y_dtype == BG_DTYPE_F32 && d % 4 == 0 && ldh % 4 == 0 && (uintptr_t)yp % 16 == 0 && (uintptr_t)out % 16 == 0 &&
+        (!shared || (uintptr_t)shared % 16 == 0)) {
+        const int tv = d / 4 >= 384 ? 384 : ((d / 4 + 31) / 32) * 32;
+        BG_DISPATCH_DTYPE(h_dtype, TH, launch(route_combine_ext_vec4_kernel<TH>, dim3(T), dim3(tv), 0, stream, (const float*)yp, weights,
+                                              row_of, ids, n_real, (const TH*)h, ldh, shared, sg, sg_float, sg_stride, out, T, d, top));
+        BG_LAUNCH_CHECK();
+        return BG_OK;
+    }
     BG_DISPATCH_DTYPE(y_dtype, TY, BG_DISPATCH_DTYPE(h_dtype, TH,
         launch(route_combine_ext_kernel<TY, TH>, dim3(T), dim3(threads), 0, stream, (const TY*)yp, weights, row_of, ids, n_real,
-               (const TH*)h, ldh, shared, sg, sg_stride, out, T, d, top)));
+               (const TH*)h, ldh, shared, sg, sg_float, sg_stride, out, T, d, top)));
     BG_LAUNCH_CHECK();
     return BG_OK;
 }
@@ -522,6 +594,14 @@ extern "C" int bg_glu_clamped(const void* gu, int gu_dtype, int ld, void* out, i
     if (ld < 2 * n) return BG_ERR_SHAPE;
     const size_t total = (size_t)rows * n;
     if ((total + 255) / 256 > 0x7fffffffULL) return BG_ERR_SHAPE;
+    if (n % 8 == 0 && ld % 8 == 0 && (uintptr_t)gu % 16 == 0 && (uintptr_t)out % 16 == 0) {
+        const size_t total8 = total / 8;
+        BG_DISPATCH_DTYPE(gu_dtype, TI, BG_DISPATCH_DTYPE(out_dtype, TO,
+            launch(glu_clamped_vec8_kernel<TI, TO>, dim3((unsigned)((total8 + 255) / 256)), dim3(256), 0, stream, (const TI*)gu, ld,
+                   (TO*)out, total8, n, limit, alpha)));
+        BG_LAUNCH_CHECK();
+        return BG_OK;
+    }
     BG_DISPATCH_DTYPE(gu_dtype, TI, BG_DISPATCH_DTYPE(out_dtype, TO,
         launch(glu_clamped_kernel<TI, TO>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, (const TI*)gu, ld, (TO*)out,
                total, n, limit, alpha)));

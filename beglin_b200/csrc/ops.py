@@ -52,7 +52,7 @@ _SIGNATURES = {
     "bg_route": [_c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_float,
                  _c_void_p, _c_void_p, _c_void_p, _c_void_p],
     "bg_route_combine_ext": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p,
-                             _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
+                             _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
     "bg_glu_clamped": [_c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_float, _c_float, _c_void_p],
     "bg_lane_step": [_c_void_p, _c_int, _c_ll, _c_void_p, _c_int, _c_int, _c_ll, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                      _c_float, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p],
@@ -60,9 +60,10 @@ _SIGNATURES = {
     "bg_rglru_scan": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_ll,
                       _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "bg_rglru_scan_chunked": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_ll,
-                              _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_int,
+                              _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int,
                               _c_int, _c_int, _c_void_p],
     "bg_rglru_softplus": [_c_void_p, _c_int, _c_float, _c_void_p, _c_int, _c_void_p],
+    "bg_rglru_split": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
     "bg_route_sort": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
     "bg_route_gather": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "bg_route_combine": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
@@ -1541,7 +1542,7 @@ def route_combine_ext(yp: torch.Tensor, weights: torch.Tensor, row_of: torch.Ten
                       out: torch.Tensor, top: int, shared: Optional[torch.Tensor] = None, sg: Optional[torch.Tensor] = None) -> None:
     """out[t] = sum over j < top of weights[t top + j] * (yp[row_of[t top + j]] if ids[t top + j] < n_real else h[t])
     + sigmoid(sg[t]) * shared[t]: experts from n_real on return their input h [T, d] (either type, unit inner stride).
-    `shared` float32 [T, d] contiguous and `sg` float32 [T] (any stride) may be absent; without sg the shared rows are added
+    `shared` float32 [T, d] contiguous and `sg` [T] (either type, any stride) may be absent; without sg the shared rows are added
     as they are."""
     _cuda(yp, weights, row_of, ids, h, out, shared, sg)
     _i32(row_of, "row_of"); _i32(ids, "ids")
@@ -1552,12 +1553,12 @@ def route_combine_ext(yp: torch.Tensor, weights: torch.Tensor, row_of: torch.Ten
         raise KernelError("route_combine_ext: yp [T * top, d], h [T, d], out float32 [T, d], ids and weights [T * top]")
     if shared is not None and (shared.dtype != torch.float32 or tuple(shared.shape) != (T, d) or not shared.is_contiguous()):
         raise KernelError("route_combine_ext: shared float32 [T, d]")
-    if sg is not None and (shared is None or sg.dtype != torch.float32 or sg.dim() != 1 or sg.numel() != T):
-        raise KernelError("route_combine_ext: sg float32 [T] beside shared rows")
+    if sg is not None and (shared is None or sg.dim() != 1 or sg.numel() != T):
+        raise KernelError("route_combine_ext: sg [T] beside shared rows")
     with phase("router"):
         _check(lib().bg_route_combine_ext(_p(yp), _dt(yp), _p(weights), _p(row_of), _p(ids), int(n_real), _p(h), _dt(h), h.stride(0),
-                                          _p(shared), _p(sg), sg.stride(0) if sg is not None else 0, _p(out), T, d, top,
-                                          _stream()), "route_combine_ext")
+                                          _p(shared), _p(sg), _dt(sg) if sg is not None else F32,
+                                          sg.stride(0) if sg is not None else 0, _p(out), T, d, top, _stream()), "route_combine_ext")
 
 
 def glu_clamped(gate_up: torch.Tensor, out: torch.Tensor, limit: float, alpha: float = 1.702) -> None:
@@ -1631,6 +1632,18 @@ def rglru_softplus(lam: torch.Tensor, scale: float, out: torch.Tensor) -> None:
     _check(lib().bg_rglru_softplus(_p(lam), _dt(lam), float(scale), _p(out), lam.numel(), _stream()), "rglru_softplus")
 
 
+def rglru_split(u: torch.Tensor, blocks: int, out: torch.Tensor) -> None:
+    """out[b, t] = [bfloat16(u_b[t]) | bfloat16(u_b[t] - the first)] for the parts u_b of u's columns: u float32 [T, W],
+    out bfloat16 [blocks, T, 2 W / blocks]."""
+    _cuda(u, out)
+    T, W = u.shape
+    if u.dtype != torch.float32 or out.dtype != torch.bfloat16 or not u.is_contiguous() or not out.is_contiguous() \
+            or W % blocks or tuple(out.shape) != (blocks, T, 2 * (W // blocks)):
+        raise KernelError("rglru_split: u float32 [T, W], out bfloat16 [blocks, T, 2 W / blocks]")
+    with phase("scan"):
+        _check(lib().bg_rglru_split(_p(u), _p(out), T, W, blocks, _stream()), "rglru_split")
+
+
 def rglru_scan(gates: torch.Tensor, u: torch.Tensor, src: torch.Tensor, y_col: int, gate_bias_r: torch.Tensor,
                gate_bias_i: torch.Tensor, decay: torch.Tensor, state: torch.Tensor, slots: torch.Tensor, reqs: torch.Tensor,
                n_req: int, out: torch.Tensor, chunked: Optional[tuple] = None) -> None:
@@ -1666,9 +1679,10 @@ def rglru_scan(gates: torch.Tensor, u: torch.Tensor, src: torch.Tensor, y_col: i
             if n_chunks == 0:
                 return
             pq = torch.empty((n_chunks, 2, W), dtype=torch.float32, device=u.device)
+            ab = torch.empty((T, W, 2), dtype=torch.float32, device=u.device)
             _check(lib().bg_rglru_scan_chunked(_p(gates), _p(u), _p(src), src.stride(0), y_col, _p(gate_bias_r), _p(gate_bias_i),
                                                _p(decay), _p(state), state.stride(0), _p(slots), _p(chunks), n_chunks, _p(longs),
-                                               n_long, chunk_rows, _p(pq), _p(out), _dt(out), T, W, blocks, _stream()),
+                                               n_long, chunk_rows, _p(pq), _p(ab), _p(out), _dt(out), T, W, blocks, _stream()),
                    "rglru_scan_chunked")
             count_launches(2)
 

@@ -126,8 +126,9 @@ __global__ void __launch_bounds__(256) qk_norm_rope_append_kernel(QkNormRopePara
 }
 
 // The same for sizes in multiples of 8 (heads, stored widths, the rotated part's halves, the source's columns) with the
-// rotation in halves: every access moves eight values, 16 bytes of bfloat16.  A thread's eight features lie in one head
-// and on one side of the rotated part, so their partners are eight consecutive features too.
+// rotation in halves or in neighbouring pairs: every access moves eight values, 16 bytes of bfloat16.  A thread's eight
+// features lie in one head and, in halves, on one side of the rotated part, so their partners are eight consecutive
+// features too; in neighbouring pairs they are four pairs of the thread's own.
 template <typename TS, typename TQ, typename TC>
 __global__ void __launch_bounds__(256) qk_norm_rope_append_vec8_kernel(QkNormRopeParams p) {
     extern __shared__ float qk_s[];
@@ -191,7 +192,16 @@ __global__ void __launch_bounds__(256) qk_norm_rope_append_vec8_kernel(QkNormRop
         float v[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) v[e] = w ? qk_s[i + e] * inv * w[e] : qk_s[i + e];
-        if (f < p.rot) {
+        if (f < p.rot && p.interleaved) {
+            // neighbouring pairs: the thread's eight features are four pairs of its own, (f + 2k, f + 2k + 1)
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float a = v[2 * k], b = v[2 * k + 1];
+                const float c = cs[2 * (f / 2 + k)], sn = cs[2 * (f / 2 + k) + 1];
+                v[2 * k] = a * c - b * sn;
+                v[2 * k + 1] = b * c + a * sn;
+            }
+        } else if (f < p.rot) {
             const bool low = f < half;
             const int pair = low ? f : f - half, partner = low ? i + half : i - half;
             const float* wp = w ? (low ? w + half : w - half) : nullptr;
@@ -289,7 +299,7 @@ using namespace bg;
 template <typename TS, typename TQ, typename TC>
 static int qk_norm_rope_launch(const QkNormRopeParams& p, int T, cudaStream_t stream) {
     const int width = p.nh * p.hd + (p.pool ? p.nkv * (p.hd + p.vd) : 0);
-    const bool vec = !std::is_same<TQ, float>::value && !p.interleaved && p.hd % 8 == 0 && p.vd % 8 == 0 && p.rot % 16 == 0 &&
+    const bool vec = !std::is_same<TQ, float>::value && p.hd % 8 == 0 && p.vd % 8 == 0 && p.rot % (p.interleaved ? 8 : 16) == 0 &&
                      p.qs % 8 == 0 && p.ks % 8 == 0 && p.vs % 8 == 0 && p.src_stride % 8 == 0 && p.part_stride % 8 == 0 &&
                      p.q_stride % 8 == 0 && (uintptr_t)p.src % 16 == 0 && (uintptr_t)p.q_out % 16 == 0 && (uintptr_t)p.pool % 16 == 0 &&
                      (!p.wq || ((uintptr_t)p.wq % 16 == 0 && (uintptr_t)p.wk % 16 == 0)) && width > 0;

@@ -12,8 +12,8 @@
 //   rglru_scan_chunked  long portions: the rows of a request are cut into chunks; S_end = P S_begin + Q with
 //                       P = prod a, Q the chunk's walk from zero, so (1) every (chunk, channel) forms P and Q, (2) a
 //                       thread per channel walks the chunks of a request to every chunk's starting state, (3) every
-//                       (chunk, channel) walks its rows again from that state and writes the outputs.  The two walks
-//                       differ from the plain one by rounding only.
+//                       (chunk, channel) walks its rows again from that state and writes the outputs, with the rows' (a, b)
+//                       as the first walk left them.  The two walks differ from the plain one by rounding only.
 //
 // The gates' products come as [blocks][T][2 bs]: for channel c = b bs + o the recurrence gate at [b][t][o] and the
 // input gate at [b][t][bs + o].
@@ -69,6 +69,7 @@ rglru_scan_kernel(LruParams p) {
     float S = *st;
     TO* out = (TO*)p.out;
     const size_t gbase = ((size_t)blk * p.T) * (2 * p.bs) + o;
+#pragma unroll 4
     for (int j = 0; j < n; ++j) {
         const int t = row0 + j;
         float a, b;
@@ -82,7 +83,7 @@ rglru_scan_kernel(LruParams p) {
 // chunks: [n][4] = (request, first row, rows, 0); longs: [n][4] = (request, first row, rows, index of its first chunk).
 // pq: [chunks][2][W] = (P, Q) of a chunk; after the walk, [chunk][0] is the state at the chunk's start.
 __global__ void __launch_bounds__(LRU_THREADS)
-rglru_chunk_sums_kernel(LruParams p, const int* __restrict__ chunks, float* __restrict__ pq) {
+rglru_chunk_sums_kernel(LruParams p, const int* __restrict__ chunks, float* __restrict__ pq, float2* __restrict__ ab) {
     pdl_launch();
     pdl_wait();
     const int c = blockIdx.x * LRU_THREADS + threadIdx.x;
@@ -93,10 +94,12 @@ rglru_chunk_sums_kernel(LruParams p, const int* __restrict__ chunks, float* __re
     const float brc = p.br[c], bic = p.bi[c], spc = p.sp[c];
     const size_t gbase = ((size_t)blk * p.T) * (2 * p.bs) + o;
     float P = 1.0f, Q = 0.0f;
+#pragma unroll 4
     for (int j = 0; j < n; ++j) {
         const int t = row0 + j;
         float a, b;
         lru_step(p, gbase + (size_t)t * (2 * p.bs), t, c, brc, bic, spc, &a, &b);
+        ab[(size_t)t * p.W + c] = make_float2(a, b);
         P *= a;
         Q = fmaf(a, Q, b);
     }
@@ -125,25 +128,40 @@ rglru_chunk_walk_kernel(LruParams p, const int* __restrict__ longs, int chunk_ro
 
 template <typename TO>
 __global__ void __launch_bounds__(LRU_THREADS)
-rglru_chunk_out_kernel(LruParams p, const int* __restrict__ chunks, const float* __restrict__ pq) {
+rglru_chunk_out_kernel(LruParams p, const int* __restrict__ chunks, const float* __restrict__ pq, const float2* __restrict__ ab) {
     pdl_launch();
     pdl_wait();
     const int c = blockIdx.x * LRU_THREADS + threadIdx.x;
     if (c >= p.W) return;
     const int ch = blockIdx.y;
     const int row0 = chunks[ch * 4 + 1], n = chunks[ch * 4 + 2];
-    const int blk = c / p.bs, o = c - blk * p.bs;
-    const float brc = p.br[c], bic = p.bi[c], spc = p.sp[c];
-    const size_t gbase = ((size_t)blk * p.T) * (2 * p.bs) + o;
     TO* out = (TO*)p.out;
     float S = pq[((size_t)ch * 2) * p.W + c];
+#pragma unroll 4
     for (int j = 0; j < n; ++j) {
         const int t = row0 + j;
-        float a, b;
-        lru_step(p, gbase + (size_t)t * (2 * p.bs), t, c, brc, bic, spc, &a, &b);
-        S = fmaf(a, S, b);
+        const float2 s = ab[(size_t)t * p.W + c];              // (a, b) of the row, as the first walk formed them
+        S = fmaf(s.x, S, s.y);
         out[(size_t)t * p.W + c] = from_float<TO>(S * gelu_tanh32(p.src[(size_t)t * p.src_stride + p.y_col + c]));
     }
+}
+
+// u [T][W] float -> x2 [blocks][T][2 bs] bfloat16: per part the rounding of u to bfloat16 followed by the rounding of what
+// the first rounding left out.  A product of x2 with a part's matrix repeated twice along its inner size is then the
+// product of u itself to sixteen bits, with float accumulation, on the tensor cores.
+__global__ void rglru_split_kernel(const float* __restrict__ u, __nv_bfloat16* __restrict__ x2, int T, int W, int bs) {
+    pdl_launch();
+    pdl_wait();
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)T * W) return;
+    const int t = (int)(idx / W), c = (int)(idx - (size_t)t * W);
+    const int blk = c / bs, o = c - blk * bs;
+    const float v = u[idx];
+    const __nv_bfloat16 hi = __float2bfloat16_rn(v);
+    const __nv_bfloat16 lo = __float2bfloat16_rn(v - __bfloat162float(hi));
+    __nv_bfloat16* dst = x2 + ((size_t)blk * T + t) * (2 * bs);
+    dst[o] = hi;
+    dst[bs + o] = lo;
 }
 
 // sp[c] = scale * softplus(lam[c]), float: log(1 + e^x), as x for large x.
@@ -188,11 +206,11 @@ extern "C" int bg_rglru_scan(const float* gates, const float* u, const float* sr
 }
 
 // The long requests of a step in chunks of `chunk_rows` rows: chunks [n_chunks][4], longs [n_long][4], pq float
-// [n_chunks][2][W] of the caller's.
+// [n_chunks][2][W] and ab float [T][W][2] of the caller's.
 extern "C" int bg_rglru_scan_chunked(const float* gates, const float* u, const float* src, int src_stride, int y_col,
                                      const float* br, const float* bi, const float* sp, float* state, long long slot_stride,
                                      const int* slots, const int* chunks, int n_chunks, const int* longs, int n_long,
-                                     int chunk_rows, float* pq, void* out, int out_dtype, int T, int W, int blocks,
+                                     int chunk_rows, float* pq, float* ab, void* out, int out_dtype, int T, int W, int blocks,
                                      cudaStream_t stream) {
     if (n_chunks <= 0 || n_long <= 0 || T <= 0) return BG_OK;
     if (n_chunks > 65535 || n_long > 65535 || chunk_rows <= 0) return BG_ERR_SHAPE;
@@ -200,12 +218,21 @@ extern "C" int bg_rglru_scan_chunked(const float* gates, const float* u, const f
     const int rc = lru_params(&p, gates, u, src, src_stride, y_col, br, bi, sp, state, slot_stride, slots, out, T, W, blocks);
     if (rc != BG_OK) return rc;
     const unsigned bx = (W + LRU_THREADS - 1) / LRU_THREADS;
-    launch(rglru_chunk_sums_kernel, dim3(bx, n_chunks), dim3(LRU_THREADS), 0, stream, p, chunks, pq);
+    launch(rglru_chunk_sums_kernel, dim3(bx, n_chunks), dim3(LRU_THREADS), 0, stream, p, chunks, pq, (float2*)ab);
     BG_LAUNCH_CHECK();
     launch(rglru_chunk_walk_kernel, dim3(bx, n_long), dim3(LRU_THREADS), 0, stream, p, longs, chunk_rows, pq);
     BG_LAUNCH_CHECK();
     BG_DISPATCH_DTYPE(out_dtype, TO, launch(rglru_chunk_out_kernel<TO>, dim3(bx, n_chunks), dim3(LRU_THREADS), 0, stream, p, chunks,
-                                            (const float*)pq));
+                                            (const float*)pq, (const float2*)ab));
+    BG_LAUNCH_CHECK();
+    return BG_OK;
+}
+
+extern "C" int bg_rglru_split(const float* u, void* x2, int T, int W, int blocks, cudaStream_t stream) {
+    if (T <= 0) return BG_OK;
+    if (W <= 0 || blocks <= 0 || W % blocks != 0) return BG_ERR_SHAPE;
+    const size_t n = (size_t)T * W;
+    launch(rglru_split_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, u, (__nv_bfloat16*)x2, T, W, W / blocks);
     BG_LAUNCH_CHECK();
     return BG_OK;
 }

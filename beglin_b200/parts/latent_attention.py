@@ -177,7 +177,7 @@ class LatentAttention:
             h = h.tensor()
         s, ctx = self.spec, self.ctx
         T, H = batch.n_rows, s.n_heads
-        down = self.down(h, out_dtype=torch.float32)                    # [T, q_rank (+ kv_rank + rot) (+ H)]
+        down = self.down.full_f32(h)                                    # [T, q_rank (+ kv_rank + rot) (+ H)]
         cos_sin = self.position.table(batch) if self.rot_dims else None
         if self.direct_q:
             ops.latent_append(down, self.kv_col, s.kv_rank, s.rot_dim, self.rot_dims, self.kv_norm, s.eps, cos_sin,

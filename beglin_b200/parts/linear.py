@@ -60,6 +60,13 @@ class Linear:
         """x is [T, in] in the compute type; the result is [T, out] in `out_dtype` (default: compute type)."""
         return self._run(x, out_dtype or self.ctx.compute_dtype, False)
 
+    def full_f32(self, x: torch.Tensor) -> torch.Tensor:
+        """The complete product [T, out] as float32: from the fused product of few rows where it runs (one kernel, the
+        ranges of the inner size added inside a cluster), else as `__call__` gives it."""
+        if self.fuses(x.shape[0]) and x.dtype == torch.bfloat16 and x.stride(1) == 1 and x.stride(0) % 8 == 0:
+            return self.of(x)
+        return self._run(x, torch.float32, False)
+
     def partial(self, x: torch.Tensor) -> torch.Tensor:
         """The product for a consumer kernel of this package (add_rmsnorm, swiglu, rope_kv_append), which
         takes either [T, out] or float partial sums [parts, T, out] over ranges of the inner size and

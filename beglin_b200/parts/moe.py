@@ -137,10 +137,11 @@ class RoutedExperts:
         shared = gate = None
         if s.shared is not None:
             im = s.shared.intermediate
-            gu = self.shared_up(h, out_dtype=torch.float32)         # [T, gate | up (| the gate's number, zeros)]
+            # [T, gate | up (| the gate's number, zeros)]: float from the fused product of few rows, else in the compute type
+            gu = self.shared_up.full_f32(h) if self.shared_up.fuses(T) else self.shared_up(h)
             act = torch.empty((T, im), dtype=ct, device=dev)
             ops.glu_clamped(gu, act, s.shared.limit)
-            shared = self.shared_down(act, out_dtype=torch.float32)
+            shared = self.shared_down.full_f32(act)
             gate = gu[:, 2 * im] if s.shared.gated else None
         out = torch.empty((T, s.hidden), dtype=torch.float32, device=dev)
         ops.route_combine_ext(yp, weights.view(-1), row_of, ids.view(-1), s.experts, h, out, s.top, shared=shared, sg=gate)

@@ -9,8 +9,10 @@ from S = 0 at a request's start, and the result is W_o (S * gelu_tanh(y)).
 The state S and the last taps - 1 inputs of the convolution are per-request state of fixed size (one slot of the cache
 manager's slab, float32, zero when the request starts): a step continues each request from its slot, however the request's
 tokens are cut into steps and whatever else the step holds.  Everything that enters the recurrence is float in both number
-formats: the input product comes out as float, the convolution, the gates' products (CUDA cores, every output summed in
-index order), sigmoids, softplus, decay, step and state are float.  Portions of at least `CHUNK_FROM` rows of a request walk
+formats: the input product comes out as float, the convolution, the gates' products, sigmoids, softplus, decay, step and
+state are float.  The gates' products run on the CUDA cores in float32 steps (every output summed in index order); in
+bfloat16 steps on the tensor cores, with u cut into two bfloat16 numbers that together hold sixteen bits of it, against the
+matrices in bfloat16, accumulated in float.  Portions of at least `CHUNK_FROM` rows of a request walk
 the recurrence in chunks that are joined by a scan over the chunks' (product of decays, sum); shorter ones and single
 tokens walk it row by row, so two ways of cutting a prompt differ by the rounding of those sums.
 """
@@ -64,6 +66,12 @@ class RGLRU:
         self.conv_w, self.conv_b = f32(tensors["conv.weight"]), f32(tensors["conv.bias"])
         # per part the two gates' matrices one above the other: [blocks, 2 bs, bs], float
         self.gate_w = f32(torch.cat([tensors["gate_r.weight"], tensors["gate_i.weight"]], dim=1))
+        # bfloat16 steps: the gates' products on the tensor cores, from u cut into two bfloat16 numbers (sixteen bits of it)
+        # against the matrices in bfloat16 repeated along the inner size; accumulation and result are float
+        self.gate_w2 = None
+        if ctx.compute_dtype == torch.bfloat16 and (W // spec.blocks) % 8 == 0:
+            w = ctx.matrix(self.gate_w)
+            self.gate_w2 = torch.cat([w, w], dim=2).transpose(1, 2).contiguous()      # [blocks, 2 bs (inner), 2 bs (out)]
         self.bias_r, self.bias_i = f32(tensors["gate_r.bias"]).view(-1), f32(tensors["gate_i.bias"]).view(-1)
         self.decay = torch.empty((W,), dtype=torch.float32, device=ctx.device)
         with torch.cuda.device(ctx.device):
@@ -78,13 +86,19 @@ class RGLRU:
             h = h.tensor()
         s, ctx = self.spec, self.ctx
         T, W, B = batch.n_rows, s.width, s.blocks
-        proj = self.in_proj(h, out_dtype=torch.float32)                 # [T, y | x], biases added
+        proj = self.in_proj.full_f32(h)                                 # [T, y | x], biases added
         reqs, n_req = batch.query_blocks(1 << 30)                       # one (request, first row, rows) per request
         u = torch.empty((T, W), dtype=torch.float32, device=h.device)
         ops.conv_silu(proj, W, W, self.conv_w, self.conv_b, cache.state, W, cache.slots, batch.row_req, reqs, n_req, u,
                       activation="none")
-        gates = torch.empty((B, T, 2 * (W // B)), dtype=torch.float32, device=h.device)
-        ops.gemm_f32_nt_batched(u.view(T, B, W // B).transpose(0, 1), self.gate_w, gates)
+        if self.gate_w2 is not None:
+            x2 = torch.empty((B, T, 2 * (W // B)), dtype=torch.bfloat16, device=h.device)
+            ops.rglru_split(u, B, x2)
+            with ops.phase("proj_heads"):
+                gates = torch.bmm(x2, self.gate_w2, out_dtype=torch.float32)
+        else:
+            gates = torch.empty((B, T, 2 * (W // B)), dtype=torch.float32, device=h.device)
+            ops.gemm_f32_nt_batched(u.view(T, B, W // B).transpose(0, 1), self.gate_w, gates)
         out = torch.empty((T, W), dtype=ctx.compute_dtype, device=h.device)
         if max(batch.lens) < self.CHUNK_FROM:
             ops.rglru_scan(gates, u, proj, 0, self.bias_r, self.bias_i, self.decay, cache.state, cache.slots, reqs, n_req, out)

@@ -408,9 +408,32 @@ def sofudra_config(width, heads, layers, vocab=32768):
             "layers": [{"type": "attention" if i == 0 else "parallel", "mixer": first if i == 0 else par, "mlp": ff} for i in range(n)]}
 
 
+# The Tuzupel decoder beside another design at equal layer sizes (--design tuzupel): the residual in two lanes; layers in the
+# order attention, latent attention, recurrence, attention, ...: grouped-query attention with heads of 128 features normed
+# one by one, half of every head rotated in neighbouring pairs with band-scaled frequencies, blocks of 1,024 positions and a
+# learned sink; attention through a latent of 512 features (width / 4 up to width 2048) with heads of 128 and a window of
+# 1,024; a gated linear recurrence of the model's width in parts of 256 channels behind a convolution of 4 taps.  Every
+# layer has eight routed experts with a gate branch of which two are chosen, two identity experts beside them and a shared
+# expert; the chosen two and the shared one together have the weights of the Qwen2 layer's feed-forward.  Random weights.
+def tuzupel_config(width, heads, layers, vocab=32768):
+    kv = max(1, heads // 4 if heads % 4 == 0 and heads > 12 else heads // 6)
+    att = {"heads": heads, "kv_heads": kv, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": 1024},
+           "rot": {"base": 500000.0, "dims": 64, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    lat = {"heads": heads, "dim": 128, "vdim": 128, "kv_rank": width // 4 if width <= 2048 else 512, "scale": 128 ** -0.5,
+           "mask": {"size": 1024}}
+    rec = {"width": width, "blocks": width // 256, "conv": 4}
+    im = (8 * width // 3) // 128 * 128
+    moe = {"kind": "moe", "expert": {"ff": (im // 4) // 64 * 64, "limit": 7.0},
+           "router": {"experts": 8, "identity": 2, "scale": 2.5, "top": 2}, "shared": {"ff": (im // 2) // 64 * 64, "limit": 7.0}}
+    kinds = [("attention", att), ("latent_attention", lat), ("rglru", rec)]
+    return {"architecture": "Tuzupel", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "streams": 2, "logit_softcap": 30.0,
+            "layers": [{"type": kinds[i % 3][0], "mixer": kinds[i % 3][1], "mlp": moe} for i in range(layers)]}
+
+
 DESIGN_SIZES = {"1536": (1536, 12, 8), "4096": (4096, 32, 4)}      # width -> (width, heads, layers)
 DESIGNS = {"sukisun": lambda w, h, l: sukisun_config(w, h, l), "nadilorn": lambda w, h, l: nadilorn_config(w, h, l),
-           "nadilorn-v64": lambda w, h, l: nadilorn_config(w, h, l, vdim=64), "sofudra": lambda w, h, l: sofudra_config(w, h, l)}
+           "nadilorn-v64": lambda w, h, l: nadilorn_config(w, h, l, vdim=64), "sofudra": lambda w, h, l: sofudra_config(w, h, l),
+           "tuzupel": lambda w, h, l: tuzupel_config(w, h, l)}
 BESIDE = dict(DESIGNS, qwen2=lambda w, h, l: qwen2_like(w, h, l))
 
 
