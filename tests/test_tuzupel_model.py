@@ -149,3 +149,43 @@ def test_trace_program(model_root, tmp_path):
                 r += 1
             held[e["id"]] = start + len(e["tokens"])
         assert r == rows.shape[0]
+
+
+def test_command_line_greedy(model_root, tmp_path):
+    """`qwen_infer greedy N` on a Tuzupel folder: the registry picks the architecture from config.json, and the
+    tokens are those of Engine.generate."""
+    folder = make_model(model_root, "even", seed=4, dtype=torch.bfloat16)
+    prompt = seeded_ids(21, CONFIGS["even"][0]["vocab"], 5)
+    path = tmp_path / "prompt.i32"
+    np.asarray(prompt, dtype="<i4").tofile(path)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, QWEN_BASE=folder, QWEN_PROMPT=str(path), QWEN_SAFETENSORS_MAXSEQ="128", QWEN_DTYPE="fp32")
+    r = subprocess.run([sys.executable, os.path.join(root, "bin", "qwen_infer"), "greedy", "6"], env=env, capture_output=True,
+                       text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    line = [l for l in r.stdout.splitlines() if l.startswith("greedy:")][0]
+    toks = [int(t) for t in line.split(":")[1].split()]
+    from beglin_b200 import Engine
+    eng = Engine.from_folder(folder, dtype="float32", max_tokens=128, max_requests=1)
+    assert toks == eng.generate([prompt], max_new_tokens=6, stop_ids=())[0]
+
+
+def test_slots_and_pages_used_again(model_root):
+    """Two state slots and five pages of 16 for six requests that come one after the other or two at a time: every
+    request's slot and pages were another request's before (NaN was in all of them at the start)."""
+    name = "odd"
+    folder = make_model(model_root, name, seed=11, dtype=torch.float32)
+    vocab = CONFIGS[name][0]["vocab"]
+    reqs = {f"q{i}": seeded_ids(n, vocab, 300 + i) for i, n in enumerate([30, 40, 25, 33, 16, 38])}
+    eng = engine_for(folder, "float32", 80, 16, max_requests=2)
+    order = list(reqs)
+    steps = []
+    for a, b in zip(order[0::2], order[1::2]):
+        ia, ib = reqs[a], reqs[b]
+        steps.append({"entries": [{"id": a, "tokens": ia[:7], "want": list(range(7))}]})
+        steps.append({"entries": [{"id": a, "tokens": ia[7:], "want": list(range(len(ia) - 7))},
+                                  {"id": b, "tokens": ib[:3], "want": [0, 1, 2]}], "end": [a]})
+        steps.append({"entries": [{"id": b, "tokens": ib[3:], "want": list(range(len(ib) - 3))}], "end": [b]})
+    got = rl.run_in_process(eng, steps)
+    eng.cache.check()
+    check_against_plain(got, folder, reqs, TOL_F32)
