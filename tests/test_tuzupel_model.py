@@ -189,3 +189,28 @@ def test_slots_and_pages_used_again(model_root):
     got = rl.run_in_process(eng, steps)
     eng.cache.check()
     check_against_plain(got, folder, reqs, TOL_F32)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_long_portion_replayed_as_a_graph(model_root, dtype):
+    """A portion of 300 tokens of one request in a shape that came before is replayed as a CUDA graph (the engine's own
+    rule): three requests of that shape one after the other, the third behind a first portion of its own so that the graph
+    runs at other positions, windows, blocks and chunk states than it was captured at; every one against the plain logits."""
+    name = "even"
+    folder = make_model(model_root, name, seed=31, dtype=stored(dtype))
+    vocab = CONFIGS[name][0]["vocab"]
+    reqs = {"a": seeded_ids(300, vocab, 1), "b": seeded_ids(300, vocab, 2), "c": seeded_ids(341, vocab, 3)}
+    want = [0, 100, 299]
+    eng = engine_for(folder, dtype, 384, 16, max_requests=2)
+    steps = [{"entries": [{"id": "a", "tokens": reqs["a"], "want": want}], "end": ["a"]},
+             {"entries": [{"id": "b", "tokens": reqs["b"], "want": want}], "end": ["b"]},
+             {"entries": [{"id": "c", "tokens": reqs["c"][:41], "want": [40]}]},
+             {"entries": [{"id": "c", "tokens": reqs["c"][41:], "want": want}], "end": ["c"]}]
+    got = rl.run_in_process(eng, steps)
+    assert eng.portions.replays >= 2
+    tol = TOL_F32 if dtype == "float32" else TOL_BF16
+    for rid, ids in reqs.items():
+        full = plain_logits(folder, ids)
+        for (r, p), row in got.items():
+            if r == rid:
+                assert rel_err(row, full[p]) < tol * float(full.abs().max() / full[p].abs().max()), (rid, p)

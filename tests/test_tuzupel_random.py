@@ -18,15 +18,15 @@ pytestmark = pytest.mark.gpu
 def random_config(case: int, even: bool = False):
     rng = random.Random(3000 + case)
     unit = 8 if even else 1
-    width = rng.choice([64, 128, 192]) if even else rng.randrange(24, 100)
+    width = rng.choice([64, 128, 192, 200, 320]) if even else rng.randrange(24, 100)
 
     def mixer():
         kind = rng.choice(["attention", "latent_attention", "rglru"])
         if kind == "attention":
             kv = rng.choice([1, 1, 2, 3])
             heads = kv * rng.choice([1, 1, 2, 3, 4])
-            dim = rng.choice([32, 64, 128]) if even else 2 * rng.randrange(2, 20)
-            vdim = rng.choice([dim, dim, 16, 32, 64]) if even else rng.choice([dim, rng.randrange(1, 40)])
+            dim = rng.choice([32, 64, 128, 48, 80, 96]) if even else 2 * rng.randrange(2, 20)
+            vdim = rng.choice([dim, dim, 16, 32, 64, 40]) if even else rng.choice([dim, rng.randrange(1, 40)])
             rot = rng.choice([None, dim, 2 * rng.randrange(1, dim // 2 + 1)])
             scaling = rng.choice([None, (rng.choice([1.0, 2.0, 3.7, 8.0]), rng.choice([1.0, 0.5, 2.0]), rng.choice([4.0, 24.0]),
                                          rng.choice([16, 64, 512]))])
@@ -35,9 +35,9 @@ def random_config(case: int, even: bool = False):
                         base=rng.choice([10.0, 1000.0, 5e5]), scaling=scaling)
         if kind == "latent_attention":
             heads = rng.randrange(1, 6)
-            dim = rng.choice([32, 64, 128]) if even else rng.randrange(3, 40)
-            vdim = rng.choice([dim, 16, 64]) if even else rng.randrange(1, 40)
-            rank = rng.choice([32, 64, 96, 160]) if even else rng.randrange(2, 50)
+            dim = rng.choice([32, 64, 128, 48, 24]) if even else rng.randrange(3, 40)
+            vdim = rng.choice([dim, 16, 64, 40]) if even else rng.randrange(1, 40)
+            rank = rng.choice([32, 64, 96, 160, 48, 200]) if even else rng.randrange(2, 50)
             return lat(heads, dim, vdim, rank, rng.uniform(0.3, 2.0) / dim ** 0.5,
                        window=rng.choice([None, 1, 2, rng.randrange(3, 20), rng.randrange(20, 200)]))
         blocks = rng.randrange(1, 6)
