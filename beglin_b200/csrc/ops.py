@@ -1001,17 +1001,19 @@ def rmsnorm_slice(src: torch.Tensor, col0: int, n: int, weight: torch.Tensor, ep
                                       _dt(out), out.stride(0), src.shape[0], _stream()), "rmsnorm_slice")
 
 
-def gate_heads(src: torch.Tensor, gate: torch.Tensor, gate_col0: int, out: torch.Tensor) -> None:
-    """out[t, h * vd + j] = src[h, t, j] * sigmoid(gate[t, gate_col0 + h]); src is [H, T, vd]."""
+def gate_heads(src: torch.Tensor, gate: Optional[torch.Tensor], gate_col0: int, out: torch.Tensor) -> None:
+    """out[t, h * vd + j] = src[h, t, j] * sigmoid(gate[t, gate_col0 + h]); src is [H, T, vd].  Without `gate` the heads
+    are put row by row as they are."""
     _cuda(src, gate, out)
     H, T, vd = src.shape
-    if src.stride(2) != 1 or gate.stride(1) != 1 or gate_col0 + H > gate.shape[1] or gate.shape[0] < T:
+    if src.stride(2) != 1 or (gate is not None and (gate.stride(1) != 1 or gate_col0 + H > gate.shape[1] or gate.shape[0] < T)):
         raise KernelError("gate_heads: src [H, T, vd] with unit inner stride, gate rows that hold H values from gate_col0")
     if tuple(out.shape) != (T, H * vd) or not out.is_contiguous():
         raise KernelError(f"gate_heads: out is {tuple(out.shape)}, expected {(T, H * vd)}")
     with phase("activation"):
-        _check(lib().bg_gate_heads(_p(src), _dt(src), src.stride(0), src.stride(1), _p(gate), _dt(gate), gate.stride(0),
-                                   gate_col0, _p(out), _dt(out), T, H, vd, _stream()), "gate_heads")
+        _check(lib().bg_gate_heads(_p(src), _dt(src), src.stride(0), src.stride(1), _p(gate), _dt(gate) if gate is not None else F32,
+                                   gate.stride(0) if gate is not None else 0, gate_col0, _p(out), _dt(out), T, H, vd, _stream()),
+               "gate_heads")
 
 
 def gemm_f32_nt_batched(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:

@@ -219,7 +219,7 @@ __global__ void rmsnorm_slice_kernel(const TI* __restrict__ src, int src_stride,
 }
 
 // out[t, h * vd + j] = src[h][t][j] * sigmoid(gate[t, gate_col0 + h]): head-major results put row by row,
-// each head scaled by its gate.
+// each head scaled by its gate (without `gate`: put row by row as they are).
 template <typename TI, typename TG, typename TO>
 __global__ void gate_heads_kernel(const TI* __restrict__ src, size_t src_head_stride, int src_row_stride,
                                   const TG* __restrict__ gate, int gate_stride, int gate_col0, TO* __restrict__ out,
@@ -232,8 +232,7 @@ __global__ void gate_heads_kernel(const TI* __restrict__ src, size_t src_head_st
     const int j = (int)(i % vd);
     const int h = (int)((i / vd) % H);
     const int t = (int)(i / ((size_t)vd * H));
-    const float g = to_float(gate[(size_t)t * gate_stride + gate_col0 + h]);
-    const float s = 1.0f / (1.0f + expf(-g));
+    const float s = gate ? 1.0f / (1.0f + expf(-to_float(gate[(size_t)t * gate_stride + gate_col0 + h]))) : 1.0f;
     out[i] = from_float<TO>(to_float(src[(size_t)h * src_head_stride + (size_t)t * src_row_stride + j]) * s);
 }
 
@@ -251,8 +250,7 @@ __global__ void gate_heads_vec8_kernel(const TI* __restrict__ src, size_t src_he
     const int j = (int)(i % v8);
     const int h = (int)((i / v8) % H);
     const int t = (int)(i / ((size_t)v8 * H));
-    const float g = to_float(gate[(size_t)t * gate_stride + gate_col0 + h]);
-    const float sg = 1.0f / (1.0f + expf(-g));
+    const float sg = gate ? 1.0f / (1.0f + expf(-to_float(gate[(size_t)t * gate_stride + gate_col0 + h]))) : 1.0f;
     float v[8];
     load8(src + (size_t)h * src_head_stride + (size_t)t * src_row_stride + j * 8, v);
 #pragma unroll

@@ -210,10 +210,7 @@ class LatentAttention:
                              self.scale, o_lat, ctx.status, mma_stages=stages, window=self.window)
         v = self._per_head(o_lat, self.v_up, ctx.compute_dtype)        # [H, T, vdim]
         out = torch.empty((T, H * s.vdim), dtype=ctx.compute_dtype, device=h.device)
-        if s.gated:
-            ops.gate_heads(v, down, self.gate_col, out)
-        else:
-            out.view(T, H, s.vdim).copy_(v.transpose(0, 1))
+        ops.gate_heads(v, down if s.gated else None, self.gate_col, out)      # (without gates: the heads row by row)
         return self._result(out, stream)
 
     def _result(self, heads: torch.Tensor, stream: Optional[ResidualStream]) -> Optional[torch.Tensor]:
