@@ -524,13 +524,22 @@ extern "C" int bg_route(const void* h, int h_dtype, int ldh, const float* W, int
     const size_t smem = (size_t)ROUTE_TOKENS * E * sizeof(float);
     if (smem > 40 * 1024) return BG_ERR_UNSUPPORTED;
     const dim3 grid((T + ROUTE_TOKENS - 1) / ROUTE_TOKENS), block(32 * ROUTE_TOKENS);
-    if (d % 8 == 0 && ldh % 8 == 0 && (uintptr_t)h % 16 == 0 && (uintptr_t)W % 16 == 0 && T <= 256)
-        BG_DISPATCH_DTYPE(h_dtype, TI, launch(route_vec8_kernel<TI, 1, 1>, dim3(T), block, (size_t)E * sizeof(float), stream,
-                                              (const TI*)h, ldh, W, T, d, E, top, rule, ids, weights, logits_out));
-    else if (d % 8 == 0 && ldh % 8 == 0 && (uintptr_t)h % 16 == 0 && (uintptr_t)W % 16 == 0)
-        BG_DISPATCH_DTYPE(h_dtype, TI, launch(route_vec8_kernel<TI, ROUTE_TOKENS, 4>, grid, block, smem, stream, (const TI*)h, ldh, W,
-                                              T, d, E, top, rule, ids, weights, logits_out));
-    else
+    // experts a warp takes at a time in steps of few tokens: as many as let a token's experts go through in one pass (the loads
+    // of a pass are all on their way together; every expert's sum keeps its own order, so the logits are the same bits: 9.3 ->
+    // 7.8 us for ten router outputs)
+    const bool vec = d % 8 == 0 && ldh % 8 == 0 && (uintptr_t)h % 16 == 0 && (uintptr_t)W % 16 == 0;
+#define BG_ROUTE_VEC(TPB, G, GRID, SMEM)                                                                                \
+    BG_DISPATCH_DTYPE(h_dtype, TI, launch(route_vec8_kernel<TI, TPB, G>, GRID, block, SMEM, stream, (const TI*)h, ldh, W, T, d, E, \
+                                          top, rule, ids, weights, logits_out))
+    if (vec && T <= 256) {
+        const size_t one = (size_t)E * sizeof(float);
+        if (E <= ROUTE_TOKENS) BG_ROUTE_VEC(1, 1, dim3(T), one);
+        else if (E <= 2 * ROUTE_TOKENS) BG_ROUTE_VEC(1, 2, dim3(T), one);
+        else BG_ROUTE_VEC(1, 4, dim3(T), one);
+    } else if (vec) {
+        BG_ROUTE_VEC(ROUTE_TOKENS, 4, grid, smem);     // (sixteen at a time: 39.7 against 25.3 us for 2,048 tokens and ten experts)
+    } else
+#undef BG_ROUTE_VEC
         BG_DISPATCH_DTYPE(h_dtype, TI, launch(route_kernel<TI>, grid, block, smem, stream, (const TI*)h, ldh, W, T, d, E, top, rule,
                                               ids, weights, logits_out));
     BG_LAUNCH_CHECK();
