@@ -2,7 +2,7 @@
 manager is asked for, and the pages a block of positions gives back."""
 import pytest
 
-from tuzupel_helpers import CONFIGS, attn, config, lat, layer, moe, rec
+from tuzupel_helpers import CONFIGS, attn, config, lat, layer, rec
 
 
 def load(cfg):
@@ -65,9 +65,8 @@ def test_what_is_refused(change, message):
 
 
 def test_cache_needs_and_pages_given_back_in_front_of_the_newest_block():
-    import torch
     from beglin_b200.cache.manager import CacheManager
-    from beglin_b200.parts import BuildContext, registry
+    from beglin_b200.parts import registry
     from beglin_b200.parts.cache_need import FixedStateNeed, PagedKVNeed, PagedLatentNeed
     cfg = config(50, 32, 1e-5, [layer(attn(2, 1, 8, 4, 0.3, block=40)), layer(lat(2, 8, 8, 12, 0.3, window=20)), layer(rec(10, 2, 3)),
                                 layer(attn(2, 2, 8, 8, 0.3))])

@@ -157,10 +157,10 @@ def test_router_scores_choice_bias_and_constant(T, d, E, top, mode):
         assert ids[t].tolist() == order, t
         assert rel_err(w[t], 2.5 * s[t, order]) < 2e-5
     # equal scores: the lower index first
-    ids2 = torch.empty(1, 2, dtype=torch.int32, device=DEV)
-    w2 = torch.empty(1, 2, device=DEV)
-    o.route(torch.zeros(1, d, device=DEV), W.to(DEV), 2, ids2, w2, sigmoid=mode) if E >= 2 else None
     if E >= 2:
+        ids2 = torch.empty(1, 2, dtype=torch.int32, device=DEV)
+        w2 = torch.empty(1, 2, device=DEV)
+        o.route(torch.zeros(1, d, device=DEV), W.to(DEV), 2, ids2, w2, sigmoid=mode)
         assert ids2[0].tolist() == [0, 1]
 
 
