@@ -16,13 +16,15 @@ __device__ __forceinline__ float silu32(float z) { return z / (1.0f + expf(-z));
 __device__ __forceinline__ float sigmoid32(float z) { return 1.0f / (1.0f + expf(-z)); }
 
 // out[t, c] = silu(b[c] + sum_j w[c, j] * in(t - (taps-1-j), c)), in(.) taken from the step's rows of the same
-// request or, further back, from the slot's conv state.  src row = [.. | channels from col0 | ..].
+// request or, further back, from the slot's conv state.  src row = [.. | channels from col0 | ..].  `src_bias` [channels]
+// (may be null) is added to every input taken from the step's rows, and the state keeps inputs with it: what lies before a
+// request's start stays zero.
 template <typename TI, typename TW>
 __global__ void conv_silu_kernel(const TI* __restrict__ src, int src_stride, int col0, int channels, int taps,
                                  const TW* __restrict__ w, const TW* __restrict__ b, const float* __restrict__ state,
                                  size_t slot_stride, size_t conv_off, const int* __restrict__ slots,
                                  const int* __restrict__ row_req, const int* __restrict__ reqs, float* __restrict__ out,
-                                 int act) {
+                                 int act, const float* __restrict__ src_bias) {
     pdl_launch();
     pdl_wait();
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
@@ -36,7 +38,7 @@ __global__ void conv_silu_kernel(const TI* __restrict__ src, int src_stride, int
     for (int k = 0; k < taps; ++k) {
         const int back = taps - 1 - k;
         float v;
-        if (back <= j) v = to_float(src[(size_t)(t - back) * src_stride + col0 + c]);
+        if (back <= j) v = to_float(src[(size_t)(t - back) * src_stride + col0 + c]) + (src_bias ? src_bias[c] : 0.0f);
         else v = st[(size_t)(taps - 1 - (back - j)) * channels + c];
         acc = fmaf(to_float(w[(size_t)c * taps + k]), v, acc);
     }
@@ -47,7 +49,7 @@ __global__ void conv_silu_kernel(const TI* __restrict__ src, int src_stride, int
 template <typename TI>
 __global__ void conv_state_kernel(const TI* __restrict__ src, int src_stride, int col0, int channels, int taps,
                                   float* __restrict__ state, size_t slot_stride, size_t conv_off,
-                                  const int* __restrict__ slots, const int* __restrict__ reqs) {
+                                  const int* __restrict__ slots, const int* __restrict__ reqs, const float* __restrict__ src_bias) {
     pdl_launch();
     pdl_wait();
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
@@ -60,7 +62,7 @@ __global__ void conv_state_kernel(const TI* __restrict__ src, int src_stride, in
     for (int k = 0; k < keep; ++k) {                          // reads run ahead of writes: k + n > k
         const int idx = k + n;                                // index into (old state ++ new rows)
         const float v = idx < keep ? st[(size_t)idx * channels + c]
-                                   : to_float(src[(size_t)(row0 + idx - keep) * src_stride + col0 + c]);
+                                   : to_float(src[(size_t)(row0 + idx - keep) * src_stride + col0 + c]) + (src_bias ? src_bias[c] : 0.0f);
         st[(size_t)k * channels + c] = v;
     }
 }
@@ -316,7 +318,7 @@ using namespace bg;
 extern "C" int bg_conv_silu(const void* src, int src_dtype, int src_stride, int col0, int channels, int taps, const void* w,
                             const void* b, int w_dtype, float* state, long long slot_stride, long long conv_off,
                             const int* slots, const int* row_req, const int* reqs, int n_req, float* out, int n_rows,
-                            int act, cudaStream_t stream) {
+                            int act, const float* src_bias, cudaStream_t stream) {
     if (n_rows <= 0 || n_req <= 0) return BG_OK;
     if (channels <= 0 || taps < 1 || n_req > 65535) return BG_ERR_SHAPE;
     const unsigned bx = (unsigned)((channels + 127) / 128);
@@ -324,12 +326,12 @@ extern "C" int bg_conv_silu(const void* src, int src_dtype, int src_stride, int 
     BG_DISPATCH_DTYPE(src_dtype, TI, BG_DISPATCH_DTYPE(w_dtype, TW,
         launch(conv_silu_kernel<TI, TW>, dim3(n_rows, bx), dim3(128), 0, stream, (const TI*)src, src_stride, col0, channels,
                taps, (const TW*)w, (const TW*)b, (const float*)state, (size_t)slot_stride, (size_t)conv_off, slots, row_req,
-               reqs, out, act)));
+               reqs, out, act, src_bias)));
     BG_LAUNCH_CHECK();
     if (taps > 1) {
         BG_DISPATCH_DTYPE(src_dtype, TI,
             launch(conv_state_kernel<TI>, dim3(bx, n_req), dim3(128), 0, stream, (const TI*)src, src_stride, col0, channels,
-                   taps, state, (size_t)slot_stride, (size_t)conv_off, slots, reqs));
+                   taps, state, (size_t)slot_stride, (size_t)conv_off, slots, reqs, src_bias));
         BG_LAUNCH_CHECK();
     }
     return BG_OK;

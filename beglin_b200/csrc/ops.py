@@ -57,9 +57,9 @@ _SIGNATURES = {
     "bg_lane_step": [_c_void_p, _c_int, _c_ll, _c_void_p, _c_int, _c_int, _c_ll, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                      _c_float, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p],
     "bg_lane_fill": [_c_void_p, _c_void_p, _c_ll, _c_int, _c_void_p],
-    "bg_rglru_scan": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_ll,
+    "bg_rglru_scan": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_ll,
                       _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
-    "bg_rglru_scan_chunked": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_ll,
+    "bg_rglru_scan_chunked": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_ll,
                               _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int,
                               _c_int, _c_int, _c_void_p],
     "bg_rglru_softplus": [_c_void_p, _c_int, _c_float, _c_void_p, _c_int, _c_void_p],
@@ -134,7 +134,7 @@ _SIGNATURES = {
     "bg_latent_expand": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
     "bg_rotate_q": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_void_p],
     "bg_conv_silu": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_ll, _c_ll,
-                     _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p],
+                     _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p],
     "bg_ssm_scan": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p,
                     _c_ll, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "bg_gated_group_rmsnorm": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_float, _c_void_p, _c_int,
@@ -1187,9 +1187,10 @@ def rotate_q(q: torch.Tensor, H: int, head: int, off: int, rot_dims: int, cos_si
 # The Mamba-2 recurrence
 def conv_silu(src: torch.Tensor, col0: int, channels: int, weight: torch.Tensor, bias: torch.Tensor, state: torch.Tensor,
               conv_off: int, slots: torch.Tensor, row_req: torch.Tensor, reqs: torch.Tensor, n_req: int,
-              out: torch.Tensor, activation: str = "silu") -> None:
+              out: torch.Tensor, activation: str = "silu", src_bias: Optional[torch.Tensor] = None) -> None:
     """The causal convolution per channel with SiLU (`activation` "none": without it) over src[:, col0 : col0 + channels],
-    continued from and into the slots' conv state.  weight [channels, taps] (last column the current token's), bias [channels]; state float32
+    continued from and into the slots' conv state (`src_bias` float32 [channels], when given, is added to the rows' inputs,
+    and the state keeps them with it).  weight [channels, taps] (last column the current token's), bias [channels]; state float32
     [slots, slot size] with the conv state, (taps - 1) x channels, at conv_off; reqs int32 [n_req, 3] = (request,
     first row, rows); out float32 [T, channels]."""
     _cuda(src, weight, bias, state, slots, row_req, reqs, out)
@@ -1207,10 +1208,14 @@ def conv_silu(src: torch.Tensor, col0: int, channels: int, weight: torch.Tensor,
         raise KernelError("conv_silu: out is float32 [T, channels]")
     if activation not in ("silu", "none"):
         raise KernelError(f"conv_silu: unknown activation '{activation}' (silu, none)")
+    if src_bias is not None:
+        _cuda(src_bias)
+        if src_bias.dtype != torch.float32 or src_bias.numel() != channels or not src_bias.is_contiguous():
+            raise KernelError("conv_silu: src_bias is contiguous float32 [channels]")
     with phase("conv"):
         _check(lib().bg_conv_silu(_p(src), _dt(src), src.stride(0), col0, channels, taps, _p(weight), _p(bias), _dt(weight),
                                   _p(state), state.stride(0), conv_off, _p(slots), _p(row_req), _p(reqs), n_req, _p(out), T,
-                                  1 if activation == "silu" else 0, _stream()), "conv_silu")
+                                  1 if activation == "silu" else 0, _p(src_bias), _stream()), "conv_silu")
     if taps > 1:
         count_launches(1)
 
@@ -1648,15 +1653,17 @@ def rglru_split(u: torch.Tensor, blocks: int, out: torch.Tensor) -> None:
 
 def rglru_scan(gates: torch.Tensor, u: torch.Tensor, src: torch.Tensor, y_col: int, gate_bias_r: torch.Tensor,
                gate_bias_i: torch.Tensor, decay: torch.Tensor, state: torch.Tensor, slots: torch.Tensor, reqs: torch.Tensor,
-               n_req: int, out: torch.Tensor, chunked: Optional[tuple] = None) -> None:
+               n_req: int, out: torch.Tensor, chunked: Optional[tuple] = None, y_bias: Optional[torch.Tensor] = None) -> None:
     """The gated linear recurrence of a step.  gates float32 [blocks, T, 2 bs] (per block the recurrence gate's and the
     input gate's products), u float32 [T, W] the convolved input, src float32 rows whose columns y_col .. y_col + W are
-    the other branch, the gates' biases and `decay` (= C softplus(lam)) float32 [W], state float32 [slots, size] with
+    the other branch (`y_bias` float32 [W], when given, is added to it), the gates' biases and `decay` (= C softplus(lam)) float32 [W], state float32 [slots, size] with
     the W states first, reqs int32 [n_req, 3] = (request, first row, rows), out [T, W] in either type.  `chunked` =
     (chunks, n_chunks, longs, n_long, chunk_rows) instead of reqs: those requests' rows in chunks (`cut_long_requests`)."""
-    _cuda(gates, u, src, gate_bias_r, gate_bias_i, decay, state, slots, reqs, out)
+    _cuda(gates, u, src, gate_bias_r, gate_bias_i, decay, state, slots, reqs, out, y_bias)
     _i32(slots, "slots")
     T, W = u.shape
+    if y_bias is not None and (y_bias.dtype != torch.float32 or y_bias.numel() != W or not y_bias.is_contiguous()):
+        raise KernelError("rglru_scan: y_bias is contiguous float32 [W]")
     blocks = gates.shape[0]
     for t in (gates, u, gate_bias_r, gate_bias_i, decay):
         if t.dtype != torch.float32 or not t.is_contiguous():
@@ -1673,7 +1680,7 @@ def rglru_scan(gates: torch.Tensor, u: torch.Tensor, src: torch.Tensor, y_col: i
     with phase("scan"):
         if chunked is None:
             _i32(reqs, "reqs")
-            _check(lib().bg_rglru_scan(_p(gates), _p(u), _p(src), src.stride(0), y_col, _p(gate_bias_r), _p(gate_bias_i), _p(decay),
+            _check(lib().bg_rglru_scan(_p(gates), _p(u), _p(src), src.stride(0), y_col, _p(y_bias), _p(gate_bias_r), _p(gate_bias_i), _p(decay),
                                        _p(state), state.stride(0), _p(slots), _p(reqs), n_req, _p(out), _dt(out), T, W, blocks,
                                        _stream()), "rglru_scan")
         else:
@@ -1682,7 +1689,7 @@ def rglru_scan(gates: torch.Tensor, u: torch.Tensor, src: torch.Tensor, y_col: i
                 return
             pq = torch.empty((n_chunks, 2, W), dtype=torch.float32, device=u.device)
             ab = torch.empty((T, W, 2), dtype=torch.float32, device=u.device)
-            _check(lib().bg_rglru_scan_chunked(_p(gates), _p(u), _p(src), src.stride(0), y_col, _p(gate_bias_r), _p(gate_bias_i),
+            _check(lib().bg_rglru_scan_chunked(_p(gates), _p(u), _p(src), src.stride(0), y_col, _p(y_bias), _p(gate_bias_r), _p(gate_bias_i),
                                                _p(decay), _p(state), state.stride(0), _p(slots), _p(chunks), n_chunks, _p(longs),
                                                n_long, chunk_rows, _p(pq), _p(ab), _p(out), _dt(out), T, W, blocks, _stream()),
                    "rglru_scan_chunked")

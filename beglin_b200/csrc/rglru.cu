@@ -28,6 +28,7 @@ struct LruParams {
     const float* u;         // [T][W] the convolved input
     const float* src;       // the input product's rows; y of channel c at src[t * src_stride + y_col + c]
     int src_stride, y_col;
+    const float* by;        // [W] or null: added to y before its activation
     const float* br;        // [W] bias of the recurrence gate
     const float* bi;        // [W] bias of the input gate
     const float* sp;        // [W] C * softplus(lam), made once when the model is built
@@ -68,6 +69,7 @@ rglru_scan_kernel(LruParams p) {
     float* st = p.state + (size_t)p.slots[req] * p.slot_stride + c;
     float S = *st;
     TO* out = (TO*)p.out;
+    const float yb = p.by ? p.by[c] : 0.0f;
     const size_t gbase = ((size_t)blk * p.T) * (2 * p.bs) + o;
 #pragma unroll 4
     for (int j = 0; j < n; ++j) {
@@ -75,7 +77,7 @@ rglru_scan_kernel(LruParams p) {
         float a, b;
         lru_step(p, gbase + (size_t)t * (2 * p.bs), t, c, brc, bic, spc, &a, &b);
         S = fmaf(a, S, b);
-        out[(size_t)t * p.W + c] = from_float<TO>(S * gelu_tanh32(p.src[(size_t)t * p.src_stride + p.y_col + c]));
+        out[(size_t)t * p.W + c] = from_float<TO>(S * gelu_tanh32(p.src[(size_t)t * p.src_stride + p.y_col + c] + yb));
     }
     *st = S;
 }
@@ -147,13 +149,14 @@ rglru_chunk_out_kernel(LruParams p, const int* __restrict__ chunks, const float*
     const int ch = blockIdx.y;
     const int row0 = chunks[ch * 4 + 1], n = chunks[ch * 4 + 2];
     TO* out = (TO*)p.out;
+    const float yb = p.by ? p.by[c] : 0.0f;
     float S = pq[((size_t)ch * 2) * p.W + c];
 #pragma unroll 4
     for (int j = 0; j < n; ++j) {
         const int t = row0 + j;
         const float2 s = ab[(size_t)t * p.W + c];              // (a, b) of the row, as the first walk formed them
         S = fmaf(s.x, S, s.y);
-        out[(size_t)t * p.W + c] = from_float<TO>(S * gelu_tanh32(p.src[(size_t)t * p.src_stride + p.y_col + c]));
+        out[(size_t)t * p.W + c] = from_float<TO>(S * gelu_tanh32(p.src[(size_t)t * p.src_stride + p.y_col + c] + yb));
     }
 }
 
@@ -210,24 +213,26 @@ __global__ void rglru_softplus_kernel(const TW* __restrict__ lam, float scale, f
 
 using namespace bg;
 
-static int lru_params(LruParams* p, const float* gates, const float* u, const float* src, int src_stride, int y_col, const float* br,
+static int lru_params(LruParams* p, const float* gates, const float* u, const float* src, int src_stride, int y_col, const float* by,
+                      const float* br,
                       const float* bi, const float* sp, float* state, long long slot_stride, const int* slots, void* out, int T,
                       int W, int blocks) {
     if (W <= 0 || blocks <= 0 || W % blocks != 0 || T <= 0) return BG_ERR_SHAPE;
-    p->gates = gates; p->u = u; p->src = src; p->src_stride = src_stride; p->y_col = y_col; p->br = br; p->bi = bi; p->sp = sp;
+    p->gates = gates; p->u = u; p->src = src; p->src_stride = src_stride; p->y_col = y_col; p->by = by; p->br = br; p->bi = bi; p->sp = sp;
     p->state = state; p->slot_stride = slot_stride; p->slots = slots; p->reqs = nullptr; p->out = out; p->T = T; p->W = W;
     p->bs = W / blocks;
     return BG_OK;
 }
 
 // The requests `reqs` [n_req][3] of a step walked row by row.
-extern "C" int bg_rglru_scan(const float* gates, const float* u, const float* src, int src_stride, int y_col, const float* br,
+extern "C" int bg_rglru_scan(const float* gates, const float* u, const float* src, int src_stride, int y_col, const float* by,
+                             const float* br,
                              const float* bi, const float* sp, float* state, long long slot_stride, const int* slots,
                              const int* reqs, int n_req, void* out, int out_dtype, int T, int W, int blocks, cudaStream_t stream) {
     if (n_req <= 0 || T <= 0) return BG_OK;
     if (n_req > 65535) return BG_ERR_SHAPE;
     LruParams p;
-    const int rc = lru_params(&p, gates, u, src, src_stride, y_col, br, bi, sp, state, slot_stride, slots, out, T, W, blocks);
+    const int rc = lru_params(&p, gates, u, src, src_stride, y_col, by, br, bi, sp, state, slot_stride, slots, out, T, W, blocks);
     if (rc != BG_OK) return rc;
     p.reqs = reqs;
     const dim3 grid((W + LRU_THREADS - 1) / LRU_THREADS, n_req);
@@ -239,14 +244,14 @@ extern "C" int bg_rglru_scan(const float* gates, const float* u, const float* sr
 // The long requests of a step in chunks of `chunk_rows` rows: chunks [n_chunks][4], longs [n_long][4], pq float
 // [n_chunks][2][W] and ab float [T][W][2] of the caller's.
 extern "C" int bg_rglru_scan_chunked(const float* gates, const float* u, const float* src, int src_stride, int y_col,
-                                     const float* br, const float* bi, const float* sp, float* state, long long slot_stride,
+                                     const float* by, const float* br, const float* bi, const float* sp, float* state, long long slot_stride,
                                      const int* slots, const int* chunks, int n_chunks, const int* longs, int n_long,
                                      int chunk_rows, float* pq, float* ab, void* out, int out_dtype, int T, int W, int blocks,
                                      cudaStream_t stream) {
     if (n_chunks <= 0 || n_long <= 0 || T <= 0) return BG_OK;
     if (n_chunks > 65535 || n_long > 65535 || chunk_rows <= 0) return BG_ERR_SHAPE;
     LruParams p;
-    const int rc = lru_params(&p, gates, u, src, src_stride, y_col, br, bi, sp, state, slot_stride, slots, out, T, W, blocks);
+    const int rc = lru_params(&p, gates, u, src, src_stride, y_col, by, br, bi, sp, state, slot_stride, slots, out, T, W, blocks);
     if (rc != BG_OK) return rc;
     const unsigned bx = (W + LRU_THREADS - 1) / LRU_THREADS;
     launch(rglru_chunk_sums_kernel, dim3(bx, n_chunks), dim3(LRU_THREADS), 0, stream, p, chunks, pq, (float2*)ab);

@@ -1,6 +1,6 @@
 """A recurrent block around a real-gated linear recurrent unit (RG-LRU).
 
-One product of the mixer's input gives both branches side by side, [y | x] with their biases.  x passes a short causal
+One product of the mixer's input gives both branches side by side, [y | x]; their biases are added where its rows are read.  x passes a short causal
 convolution per channel (no activation) and becomes u; u is cut into equal parts, and in each part two square matrices
 give the gates, r = sigmoid(A_b u_b + a_b) and i = sigmoid(B_b u_b + b_b).  Per channel
     log a = -C r softplus(lam),   S <- e^(log a) S + sqrt(1 - e^(2 log a)) (i u),
@@ -60,8 +60,9 @@ class RGLRU:
         self.spec, self.ctx = spec, ctx
         W = spec.width
         f32 = lambda t: t.to(device=ctx.device, dtype=torch.float32).contiguous()
-        self.in_proj = Linear(torch.cat([tensors["y_proj.weight"], tensors["x_proj.weight"]], dim=0),
-                              torch.cat([tensors["y_proj.bias"].float(), tensors["x_proj.bias"].float()], dim=0), ctx, label="proj_in")
+        # (the branches' biases are added where the product's rows are read: by the convolution and by the walk)
+        self.in_proj = Linear(torch.cat([tensors["y_proj.weight"], tensors["x_proj.weight"]], dim=0), None, ctx, label="proj_in")
+        self.bias_y, self.bias_x = f32(tensors["y_proj.bias"]), f32(tensors["x_proj.bias"])
         self.o_proj = Linear(tensors["o_proj.weight"], None, ctx, label="proj_o")
         self.conv_w, self.conv_b = f32(tensors["conv.weight"]), f32(tensors["conv.bias"])
         # per part the two gates' matrices one above the other: [blocks, 2 bs, bs], float
@@ -86,11 +87,11 @@ class RGLRU:
             h = h.tensor()
         s, ctx = self.spec, self.ctx
         T, W, B = batch.n_rows, s.width, s.blocks
-        proj = self.in_proj.full_f32(h)                                 # [T, y | x], biases added
+        proj = self.in_proj.full_f32(h)                                 # [T, y | x] without their biases
         reqs, n_req = batch.query_blocks(1 << 30)                       # one (request, first row, rows) per request
         u = torch.empty((T, W), dtype=torch.float32, device=h.device)
         ops.conv_silu(proj, W, W, self.conv_w, self.conv_b, cache.state, W, cache.slots, batch.row_req, reqs, n_req, u,
-                      activation="none")
+                      activation="none", src_bias=self.bias_x)
         if self.gate_w2 is not None:
             x2 = torch.empty((B, T, 2 * (W // B)), dtype=torch.bfloat16, device=h.device)
             ops.rglru_split(u, B, x2)
@@ -101,13 +102,15 @@ class RGLRU:
             ops.gemm_f32_nt_batched(u.view(T, B, W // B).transpose(0, 1), self.gate_w, gates)
         out = torch.empty((T, W), dtype=ctx.compute_dtype, device=h.device)
         if max(batch.lens) < self.CHUNK_FROM:
-            ops.rglru_scan(gates, u, proj, 0, self.bias_r, self.bias_i, self.decay, cache.state, cache.slots, reqs, n_req, out)
+            ops.rglru_scan(gates, u, proj, 0, self.bias_r, self.bias_i, self.decay, cache.state, cache.slots, reqs, n_req, out,
+                           y_bias=self.bias_y)
         else:
             short, n_short, chunks, n_chunks, longs, n_long = batch.long_blocks(self.CHUNK_ROWS, self.CHUNK_FROM)
             if n_short:
-                ops.rglru_scan(gates, u, proj, 0, self.bias_r, self.bias_i, self.decay, cache.state, cache.slots, short, n_short, out)
+                ops.rglru_scan(gates, u, proj, 0, self.bias_r, self.bias_i, self.decay, cache.state, cache.slots, short, n_short, out,
+                               y_bias=self.bias_y)
             ops.rglru_scan(gates, u, proj, 0, self.bias_r, self.bias_i, self.decay, cache.state, cache.slots, None, 0, out,
-                           chunked=(chunks, n_chunks, longs, n_long, self.CHUNK_ROWS))
+                           chunked=(chunks, n_chunks, longs, n_long, self.CHUNK_ROWS), y_bias=self.bias_y)
         if stream is None:
             return self.o_proj.partial(out)
         self.o_proj.into(out, stream)
